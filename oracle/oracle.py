@@ -1,0 +1,198 @@
+"""ctypes front-end of the CPU oracle (``oracle/spconv_oracle.c``).
+
+TEST INFRASTRUCTURE ONLY: imported by the test-suite, the smoke check and the
+benchmark's ``cpu_baseline`` / ``--impl reference`` legs.  The shipped package
+never imports this module.
+
+Parity status: unpinned against the closed reference engine (no golden output
+tensors exist); pinned against dense ``torch.nn.functional.conv3d`` and the
+pair / voxel counts of the reference's input fixtures (see tests).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+
+ACT_NONE, ACT_RELU = 0, 1
+KIND_F16, KIND_I8, KIND_F32 = 0, 1, 2
+
+
+def build(force: bool = False) -> str:
+    """Compile ``liboracle.so`` next to its source (gcc, OpenMP)."""
+    so = os.path.join(_HERE, "liboracle.so")
+    src = os.path.join(_HERE, "spconv_oracle.c")
+    if force or not os.path.exists(so) or os.path.getmtime(so) < os.path.getmtime(src):
+        subprocess.run(["make", "-C", _HERE, "-B", "liboracle.so"], check=True,
+                       stdout=subprocess.DEVNULL)
+    return so
+
+
+def lib() -> C.CDLL:
+    global _LIB
+    if _LIB is None:
+        _LIB = C.CDLL(build())
+        _LIB.orc_subm_map.restype = C.c_int64
+        _LIB.orc_down_map.restype = C.c_int64
+    return _LIB
+
+
+def _p(a):
+    return a.ctypes.data_as(C.c_void_p) if a is not None else None
+
+
+def _i3(v):
+    return (C.c_int * 3)(*[int(x) for x in v])
+
+
+def num_threads() -> int:
+    return int(lib().orc_num_threads())
+
+
+def out_grid(grid, ksize, stride, pad, dil):
+    return [int(lib().orc_out_extent(int(g), int(k), int(s), int(p), int(d)))
+            for g, k, s, p, d in zip(grid, ksize, stride, pad, dil)]
+
+
+def count_duplicates(coords, grid) -> int:
+    coords = np.ascontiguousarray(coords, np.int32)
+    return int(lib().orc_count_duplicates(_p(coords), len(coords), _i3(grid)))
+
+
+def subm_map(coords, grid, ksize=(3, 3, 3), dil=(1, 1, 1), cap=None):
+    """Returns (map [KVOL, cap] int32, pairs)."""
+    coords = np.ascontiguousarray(coords, np.int32)
+    n = len(coords)
+    cap = max(n, 1) if cap is None else cap
+    kvol = int(np.prod(ksize))
+    m = np.full((kvol, cap), -1, np.int32)
+    pairs = lib().orc_subm_map(_p(coords), n, _i3(grid), _i3(ksize), _i3(dil), _p(m), cap)
+    return m, int(pairs)
+
+
+def down_map(coords, grid, ksize, stride, pad, dil=(1, 1, 1), cap=None):
+    """Returns (out_coords [n_out,4], map [KVOL, cap], pairs, out_grid)."""
+    coords = np.ascontiguousarray(coords, np.int32)
+    n = len(coords)
+    kvol = int(np.prod(ksize))
+    if cap is None:
+        cap = max(n * kvol, 1)
+        cap = min(cap, max(1, int(np.prod(out_grid(grid, ksize, stride, pad, dil)))))
+    oc = np.zeros((cap, 4), np.int32)
+    m = np.full((kvol, cap), -1, np.int32)
+    n_out = C.c_int(0)
+    og = (C.c_int * 3)()
+    pairs = lib().orc_down_map(_p(coords), n, _i3(grid), _i3(ksize), _i3(stride), _i3(pad),
+                               _i3(dil), _p(oc), _p(m), cap, C.byref(n_out), og)
+    return oc[: min(n_out.value, cap)], m, int(pairs), [int(x) for x in og], n_out.value
+
+
+def conv_f32(x, m, n_out, w, bias=None, act=ACT_NONE):
+    x = np.ascontiguousarray(x, np.float32)
+    w = np.ascontiguousarray(w, np.float32)
+    cout, kvol, cin = w.shape[0], int(np.prod(w.shape[1:-1])), w.shape[-1]
+    assert m.shape[0] == kvol and x.shape[1] == cin
+    b = None if bias is None else np.ascontiguousarray(bias, np.float32)
+    out = np.empty((n_out, cout), np.float32)
+    lib().orc_conv_f32(_p(x), _p(m), m.shape[1], n_out, kvol, cin, cout, _p(w), _p(b), act,
+                       _p(out))
+    return out
+
+
+def quantize_weights(w, amax):
+    w = np.ascontiguousarray(w, np.float32)
+    amax = np.ascontiguousarray(amax, np.float32)
+    q = np.empty(w.shape, np.int8)
+    lib().orc_quantize_weights(_p(w), w.shape[0], int(np.prod(w.shape[1:])), _p(amax), _p(q))
+    return q
+
+
+def quantize_f16(x, dynamic_range):
+    x = np.ascontiguousarray(x, np.float16)
+    q = np.empty(x.shape, np.int8)
+    inv = np.float32(127.0) / np.float32(dynamic_range)
+    lib().orc_quantize_f16(_p(x), C.c_size_t(x.size), C.c_float(inv), _p(q))
+    return q
+
+
+def _out_array(n, cout, out_kind):
+    return np.empty((n, cout), {KIND_F16: np.float16, KIND_I8: np.int8, KIND_F32: np.float32}[out_kind])
+
+
+def conv_i8(xq, m, n_out, wq, scale, bias, act, out_kind, inv_out_scale=1.0):
+    xq = np.ascontiguousarray(xq, np.int8)
+    wq = np.ascontiguousarray(wq, np.int8)
+    cout, kvol, cin = wq.shape[0], int(np.prod(wq.shape[1:-1])), wq.shape[-1]
+    assert m.shape[0] == kvol and xq.shape[1] == cin
+    scale = np.ascontiguousarray(scale, np.float32)
+    b = None if bias is None else np.ascontiguousarray(bias, np.float32)
+    out = _out_array(n_out, cout, out_kind)
+    lib().orc_conv_i8(_p(xq), _p(m), m.shape[1], n_out, kvol, cin, cout, _p(wq), _p(scale),
+                      _p(b), act, out_kind, C.c_float(inv_out_scale), _p(out))
+    return out
+
+
+def conv_f16(x, m, n_out, w, bias, act, out_kind, inv_out_scale=1.0):
+    x = np.ascontiguousarray(x, np.float16)
+    w = np.ascontiguousarray(w, np.float16)
+    cout, kvol, cin = w.shape[0], int(np.prod(w.shape[1:-1])), w.shape[-1]
+    assert m.shape[0] == kvol and x.shape[1] == cin
+    b = None if bias is None else np.ascontiguousarray(bias, np.float32)
+    out = _out_array(n_out, cout, out_kind)
+    lib().orc_conv_f16(_p(x), _p(m), m.shape[1], n_out, kvol, cin, cout, _p(w), _p(b), act,
+                       out_kind, C.c_float(inv_out_scale), _p(out))
+    return out
+
+
+def _kind(a):
+    return KIND_I8 if a.dtype == np.int8 else KIND_F16
+
+
+def add(a, a_scale, b, b_scale, relu, out_kind, inv_out_scale=1.0):
+    a = np.ascontiguousarray(a)
+    b = np.ascontiguousarray(b)
+    out = _out_array(a.shape[0], a.shape[1], out_kind)
+    lib().orc_add(_p(a), _kind(a), C.c_float(a_scale), _p(b), _kind(b), C.c_float(b_scale),
+                  C.c_size_t(a.size), int(relu), out_kind, C.c_float(inv_out_scale), _p(out))
+    return out
+
+
+def relu(x):
+    x = np.ascontiguousarray(x)
+    out = np.empty_like(x)
+    lib().orc_relu(_p(x), _kind(x), C.c_size_t(x.size), _p(out))
+    return out
+
+
+def scatter_dense(feat, coords, grid, batch=1, in_scale=1.0, perm=None):
+    feat = np.ascontiguousarray(feat)
+    coords = np.ascontiguousarray(coords, np.int32)
+    ch = feat.shape[1]
+    g = [grid[p] for p in perm] if perm is not None else list(grid)
+    out = np.empty((batch, ch, g[0], g[1], g[2]), np.float16)
+    lib().orc_scatter_dense(_p(feat), _kind(feat), C.c_float(in_scale), _p(coords), len(coords),
+                            ch, batch, _i3(grid), _i3(perm) if perm is not None else None,
+                            _p(out))
+    return out
+
+
+def voxelize(points, range6, vsize, gridxyz, max_voxels=160000, max_pts=10, order=0):
+    """points: [n, nfeat] float32 or float16.  Returns (features f16, coords i32, total)."""
+    points = np.ascontiguousarray(points)
+    kind = 1 if points.dtype == np.float16 else 0
+    if kind == 0:
+        points = points.astype(np.float32, copy=False)
+    n, nfeat = points.shape
+    feat = np.zeros((max_voxels, nfeat), np.float16)
+    coords = np.zeros((max_voxels, 4), np.int32)
+    r = (C.c_float * 6)(*[float(x) for x in range6])
+    v = (C.c_float * 3)(*[float(x) for x in vsize])
+    nv = lib().orc_voxelize(_p(points), kind, n, nfeat, r, v, _i3(gridxyz), max_voxels, max_pts,
+                            order, _p(feat), _p(coords))
+    m = min(nv, max_voxels)
+    return feat[:m], coords[:m], int(nv)
