@@ -1,0 +1,232 @@
+/*
+ * spconvb.h - C ABI of the B200 sparse-convolution library (libspconvb.so).
+ *
+ * Every entry point takes plain pointers and sizes, enqueues work on the CUDA
+ * stream it is given (a cudaStream_t passed as void*) and returns 0 on success
+ * or a negative SPCONVB_E_* / positive cudaError_t value.  Nothing here
+ * synchronises the stream unless its comment says so.
+ *
+ * Row counts live in device memory (`const uint32_t* n_ptr`): kernels read
+ * them on the device, so a whole frame runs without a host round trip and can
+ * be captured in a CUDA graph.  This is what the reference calls DDS
+ * (SparseDTensor::set_dds_num_of_points_pointer,
+ * libraries/3DSparseConvolution/libspconv/include/spconv/engine.hpp:48-49);
+ * `launch_rows` plays the role of its `fixed_launch_points`
+ * (libraries/3DSparseConvolution/src/onnx-parser.hpp:38): it only sizes the
+ * grid, every kernel strides over the rows that are really there.
+ *
+ * Device-side problems (full hash table, duplicated coordinates, more outputs
+ * than capacity, a wait that ran out) never fault: they set bits in a 4-word
+ * status block in device memory (SPCONVB_ST_*), which the host reads when it
+ * wants to.
+ *
+ * Data conventions
+ *   coords   int32 [rows][4] = (batch, c0, c1, c2)
+ *   map      int32 [kvol][cap]; map[k*cap + o] = input row of output row o
+ *            under kernel tap k, or -1.  k = (k0*K1 + k1)*K2 + k2,
+ *            in = out*stride - pad + k*dilation.
+ *   features row-major [rows][channels], int8 or fp16
+ *   weights  [Cout][kvol][Cin] (the ONNX initialiser layout written by
+ *            libraries/3DSparseConvolution/tool/centerpoint-export/funcs.py:43-60)
+ */
+#ifndef SPCONVB_H_
+#define SPCONVB_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SPCONVB_API __attribute__((visibility("default")))
+
+/* host-side error codes (returned) */
+#define SPCONVB_OK 0
+#define SPCONVB_E_ARG (-1)        /* bad argument / unsupported shape */
+#define SPCONVB_E_RANGE (-2)      /* grid too large for 32-bit voxel keys */
+#define SPCONVB_E_NOMEM (-3)
+#define SPCONVB_E_PARSE (-4)      /* model file could not be read */
+#define SPCONVB_E_UNSUPPORTED (-5)
+#define SPCONVB_E_STATE (-6)      /* call made in the wrong state */
+#define SPCONVB_E_DEVICE (-7)     /* status block reported a device-side error */
+
+/* device status bits (status[0]); status[1] = first offending row / count */
+#define SPCONVB_ST_HASH_FULL 1u
+#define SPCONVB_ST_DUPLICATE 2u
+#define SPCONVB_ST_OVERFLOW 4u    /* more rows than capacity; extra rows dropped */
+#define SPCONVB_ST_TIMEOUT 8u     /* a bounded wait inside a kernel ran out */
+#define SPCONVB_ST_COORD_RANGE 16u
+
+/* element kinds */
+#define SPCONVB_F16 0
+#define SPCONVB_I8 1
+
+/* activations */
+#define SPCONVB_ACT_NONE 0
+#define SPCONVB_ACT_RELU 1
+
+/* flags */
+#define SPCONVB_FLAG_PREZEROED 1u /* caller already zeroed table / workspace */
+
+SPCONVB_API const char* spconvb_version(void);
+SPCONVB_API const char* spconvb_error_string(int code);
+
+/* ---------------------------------------------------------------- rulebooks
+ * Replaces the closed rulebook / index-pair construction that
+ * EngineBuilder::push_sparse_conv implies through its `submanifold`,
+ * `kernel_size`, `stride`, `padding`, `dilation` and `rulebook` arguments
+ * (libraries/3DSparseConvolution/libspconv/include/spconv/engine.hpp:135-156). */
+
+/* Number of 8-byte slots of the coordinate hash table for `cap_rows` rows
+ * (power of two, load factor <= 0.5). */
+SPCONVB_API uint32_t spconvb_hash_slots(uint32_t cap_rows);
+
+/* Insert rows 0..*n_ptr-1 of `coords` into `table` (slot = (key+1)<<32 | row,
+ * 0 = empty).  Zeroes the table first unless SPCONVB_FLAG_PREZEROED. */
+SPCONVB_API int spconvb_hash_build(const int32_t* coords, const uint32_t* n_ptr, uint32_t cap,
+                                   uint32_t launch_rows, const int32_t grid[3], int32_t batch,
+                                   uint64_t* table, uint32_t slots, uint32_t flags,
+                                   uint32_t* status, void* stream);
+
+/* Submanifold map: outputs are the inputs.  map is [kvol][cap]. */
+SPCONVB_API int spconvb_subm_map(const int32_t* coords, const uint32_t* n_ptr, uint32_t cap,
+                                 uint32_t launch_rows, const int32_t grid[3], int32_t batch,
+                                 const int32_t ksize[3], const int32_t dilation[3],
+                                 const uint64_t* table, uint32_t slots, int32_t* map,
+                                 uint32_t* status, void* stream);
+
+/* Output grid of a strided conv along one axis. */
+SPCONVB_API int32_t spconvb_out_extent(int32_t in, int32_t k, int32_t stride, int32_t pad,
+                                       int32_t dilation);
+
+/* Bytes of scratch spconvb_down_map needs for an output grid. */
+SPCONVB_API size_t spconvb_down_workspace_bytes(const int32_t out_grid[3], int32_t batch);
+
+/* Strided sparse conv rulebook.  Produces the unique output coordinates in
+ * ascending ((b*G0+c0)*G1+c1)*G2+c2 order, their count (*n_out_ptr, clipped to
+ * cap_out, SPCONVB_ST_OVERFLOW on clipping), the map [kvol][cap_out] and, when
+ * out_table != NULL, the hash table of the outputs (ready for the next
+ * stage's spconvb_subm_map).  `in_table` must hold the inputs. */
+SPCONVB_API int spconvb_down_map(const int32_t* in_coords, const uint32_t* n_in_ptr,
+                                 uint32_t cap_in, uint32_t launch_rows, const int32_t in_grid[3],
+                                 int32_t batch, const int32_t ksize[3], const int32_t stride[3],
+                                 const int32_t pad[3], const int32_t dilation[3],
+                                 const uint64_t* in_table, uint32_t in_slots, void* workspace,
+                                 int32_t* out_coords, uint32_t* n_out_ptr, uint32_t cap_out,
+                                 int32_t* map, uint64_t* out_table, uint32_t out_slots,
+                                 uint32_t flags, uint32_t* status, void* stream);
+
+/* ------------------------------------------------------------- convolution
+ * Replaces the closed gather-GEMM-scatter kernel behind
+ * EngineBuilder::push_sparse_conv (engine.hpp:135-156) with its fused
+ * dequant + bias + activation + requant epilogue, and optionally the
+ * following Add(+ReLU) node (engine.hpp:100-112). */
+
+typedef struct spconvb_conv_params {
+  int32_t compute;        /* SPCONVB_I8 or SPCONVB_F16: operand type of the MMA */
+  int32_t cin;            /* input channels as stored (a power of two >= 16 bytes per row) */
+  int32_t cout;           /* 16, 32, 64 or 128 for the tensor-core path */
+  int32_t kvol;           /* kernel taps */
+  int32_t act;            /* SPCONVB_ACT_* applied to the conv result */
+  int32_t out_kind;       /* SPCONVB_I8 / SPCONVB_F16 of `out` */
+  float inv_out_scale;    /* 127 / dynamic range of the consumer (int8 out) */
+  /* fused residual add (res == NULL: none).  The conv result is first rounded
+   * to mid_kind exactly as if it had been stored, then
+   * out = store(relu?(deq(mid) + deq(res))). */
+  const void* res;
+  int32_t res_kind;
+  float res_scale;
+  int32_t mid_kind;
+  float mid_inv_scale;
+  float mid_scale;
+  int32_t res_relu;
+  int32_t force_simt;     /* use the CUDA-core kernel (any channel count) */
+} spconvb_conv_params;
+
+/* Bytes of the packed device image of a weight tensor for the tensor-core path. */
+SPCONVB_API size_t spconvb_conv_packed_bytes(int32_t compute, int32_t cin, int32_t cout,
+                                             int32_t kvol);
+
+/* Host-side packing: `w` is [cout][kvol][cin] int8 (compute I8) or fp16
+ * (compute F16) in host memory; `dst` is a host buffer of
+ * spconvb_conv_packed_bytes() to be copied to the device by the caller. */
+SPCONVB_API int spconvb_conv_pack_weights(int32_t compute, int32_t cin, int32_t cout,
+                                          int32_t kvol, const void* w, void* dst);
+
+/* 1 when the tensor-core kernel covers this shape. */
+SPCONVB_API int spconvb_conv_supported(int32_t compute, int32_t cin, int32_t cout);
+
+/* out[o,:] = epilogue(sum_k W[:,k,:] . in[map[k][o],:]).
+ * `w_plain` ([cout][kvol][cin], device) is read by the CUDA-core kernel,
+ * `w_packed` by the tensor-core kernel; either may be NULL if unused.
+ * `scale` (int8: s_in*s_w[c]) and `bias` are fp32 [cout] on the device. */
+SPCONVB_API int spconvb_conv_forward(const spconvb_conv_params* p, const void* in,
+                                     const int32_t* map, uint32_t cap,
+                                     const uint32_t* n_out_ptr, uint32_t launch_rows,
+                                     const void* w_plain, const void* w_packed,
+                                     const float* scale, const float* bias, void* out,
+                                     uint32_t* status, void* stream);
+
+/* ------------------------------------------------------------ elementwise
+ * Add / Add&ReLU / ReLU (EngineBuilder::push_add, push_relu, engine.hpp:100-112),
+ * precision changes between layers, and channel padding of the input. */
+
+SPCONVB_API int spconvb_add(const void* a, int32_t a_kind, float a_scale, const void* b,
+                            int32_t b_kind, float b_scale, int32_t channels,
+                            const uint32_t* n_ptr, uint32_t launch_rows, int32_t relu,
+                            int32_t out_kind, float inv_out_scale, void* out, void* stream);
+
+SPCONVB_API int spconvb_relu(const void* x, int32_t kind, int32_t channels, const uint32_t* n_ptr,
+                             uint32_t launch_rows, void* out, void* stream);
+
+/* Copy rows [*n_ptr][cin] to [*n_ptr][cout_pad] with zero padding and an
+ * optional precision change (fp16 -> int8 with inv_scale, int8 -> fp16 with scale). */
+SPCONVB_API int spconvb_convert(const void* x, int32_t in_kind, int32_t cin, int32_t out_kind,
+                                int32_t cout_pad, float scale_or_inv, const uint32_t* n_ptr,
+                                uint32_t launch_rows, void* out, void* stream);
+
+/* ScatterDense (+ Transpose of the spatial axes), EngineBuilder::push_dense
+ * (engine.hpp:114-123).  out is fp16 [batch][channels][g(perm0)][g(perm1)][g(perm2)]
+ * and is fully written (zeros where no voxel). */
+SPCONVB_API int spconvb_scatter_dense(const void* feat, int32_t in_kind, float in_scale,
+                                      const int32_t* coords, const uint32_t* n_ptr,
+                                      uint32_t launch_rows, int32_t channels, int32_t batch,
+                                      const int32_t grid[3], const int32_t perm[3], void* out,
+                                      void* stream);
+
+/* -------------------------------------------------------------- voxelizer
+ * Replaces buildHashKernel / voxelizationKernel / featureExtractionKernel
+ * (CUDA-CenterPoint/src/preprocess_kernels.cu:70-173 and the two copies in
+ * libraries/3DSparseConvolution/src/voxelization.cu and
+ * CUDA-BEVFusion/src/bevfusion/lidar-voxelization.cu).  Deterministic: voxel
+ * ids follow the first point of each voxel in point order and the first
+ * `max_points_per_voxel` points (by index) are averaged, which is what the
+ * reference kernels compute when they run one point at a time. */
+
+typedef struct spconvb_voxel_params {
+  float range_min[3];     /* x, y, z */
+  float range_max[3];
+  float voxel_size[3];
+  int32_t grid[3];        /* gx, gy, gz */
+  int32_t num_features;   /* <= 8 */
+  int32_t points_kind;    /* 0 = fp32 points, 1 = fp16 points */
+  int32_t max_points_per_voxel; /* <= 16 */
+  int32_t max_voxels;
+  int32_t order;          /* 0: indices (0,z,y,x); 1: indices (0,x,y,z) */
+} spconvb_voxel_params;
+
+SPCONVB_API size_t spconvb_voxelize_workspace_bytes(const spconvb_voxel_params* p,
+                                                    uint32_t max_points);
+
+/* features fp16 [max_voxels][num_features], indices int32 [max_voxels][4];
+ * *n_voxels_ptr (device) receives min(count, max_voxels). */
+SPCONVB_API int spconvb_voxelize(const spconvb_voxel_params* p, const void* points,
+                                 uint32_t num_points, void* workspace, void* features,
+                                 int32_t* indices, uint32_t* n_voxels_ptr, uint32_t* status,
+                                 void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPCONVB_H_ */

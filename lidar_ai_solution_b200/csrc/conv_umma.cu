@@ -1,0 +1,573 @@
+// Sparse convolution as an implicit GEMM on the sm_100a tensor cores.
+//
+//   out[o, :] = epilogue( sum_k  W[:, k, :] . in[map[k][o], :] )
+//
+// is a GEMM with M = output rows, N = Cout and K = kvol * Cin whose A operand
+// does not exist in memory: row o of A is the concatenation of the feature
+// rows of o's neighbours (zeros where a neighbour is absent).  The kernel is
+// persistent (one CTA per SM, tiles of 128 output rows) and warp-specialised:
+//
+//   warps 0-3  epilogue: tcgen05.ld the accumulator tile out of TMEM, apply
+//              dequant + bias + activation (+ residual add) + requant, store
+//              one output row per thread with 16-byte stores
+//   warp  4    allocates TMEM; one lane issues tcgen05.mma (kind::i8 with int32
+//              accumulators or kind::f16 with fp32 accumulators)
+//   warps 5-8  producers, one thread per tile row: gather the row's
+//              neighbours with 16-byte cp.async (zero-fill for missing ones)
+//              straight into the 128-byte-swizzled K-major layout the MMA
+//              reads; thread 0 also streams the pre-swizzled weight chunk with
+//              one bulk async copy
+//
+// K is walked in chunks of 128 bytes (one swizzle atom per row): a chunk is 8
+// taps of a 16-byte row, ..., 1 tap of a 128-byte row, or half a 256-byte row.
+// Stages cycle through a 4-deep ring guarded by mbarriers; the accumulator is
+// double-buffered in TMEM so the epilogue of tile t overlaps the MMAs of t+1.
+//
+// Every wait is bounded: a wait that runs out sets SPCONVB_ST_TIMEOUT in the
+// status block, raises a CTA-wide abort flag and all roles leave their loops,
+// drain their copies and free TMEM.
+#include "common.cuh"
+
+namespace spconvb {
+
+namespace {
+
+constexpr int kTileM = 128;
+constexpr int kStages = 4;
+constexpr int kLag = 2;  // cp.async groups in flight per producer thread
+constexpr int kChunk = 128;
+constexpr int kABytes = kTileM * kChunk;
+constexpr int kEpiWarps = 4;
+constexpr int kMmaWarp = 4;
+constexpr int kProdWarp0 = 5;
+constexpr int kProdThreads = 128;
+constexpr int kCtaThreads = 32 * 9;
+constexpr unsigned long long kWaitLimitNs = 250ull * 1000 * 1000;
+
+struct UmmaArgs {
+  const uint8_t* in;
+  const int32_t* map;
+  uint32_t cap;
+  const uint32_t* n_out_ptr;
+  const uint8_t* wpk;
+  const float* scale;
+  const float* bias;
+  const uint8_t* res;
+  uint8_t* out;
+  uint32_t* status;
+  int kvol;
+  Epilogue ep;
+};
+
+// ------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false when the CTA is aborting.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity,
+                                            volatile uint32_t* abort_flag, uint32_t* status,
+                                            uint32_t where) {
+  const unsigned long long t0 = global_ns();
+  while (true) {
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (global_ns() - t0 > kWaitLimitNs) {
+      *abort_flag = 1u;
+      set_status(status, SPCONVB_ST_TIMEOUT, where);
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
+                                          volatile uint32_t* abort_flag, uint32_t* status,
+                                          uint32_t where) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, abort_flag, status, where);
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src),
+               "r"(src_bytes)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() {
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes,
+                                         uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+          "r"(dst),
+      "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::
+                   "r"(bar)
+               : "memory");
+}
+template <bool INT8>
+__device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                     uint32_t idesc, uint32_t accumulate) {
+  if (INT8) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+        "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+        "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// K-major operand tile, 128-byte swizzle: rows are 128 bytes, groups of 8 rows
+// are 1024 bytes apart.  Field layout of the 64-bit shared-memory descriptor:
+// [0,14) address>>4, [16,30) leading offset>>4 (unused for swizzled K-major),
+// [32,46) stride offset>>4, [46,48) version = 1, [61,64) swizzle mode (2 = 128 B).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+  return (uint64_t)((saddr >> 4) & 0x3FFFu) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+
+// 32-bit instruction descriptor: [4,6) D format (1 = f32, 2 = s32), [7,10) A
+// format, [10,13) B format (f16 kind: 0 = f16; i8 kind: 1 = signed), bits 15/16
+// A/B major (0 = K), [17,23) N>>3, [24,29) M>>4.
+template <bool INT8, int COUT>
+__device__ __forceinline__ constexpr uint32_t make_idesc() {
+  return (INT8 ? ((2u << 4) | (1u << 7) | (1u << 10)) : (1u << 4)) |
+         ((uint32_t)(COUT >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+}
+
+template <int COUT>
+constexpr size_t umma_smem_bytes() {
+  return 1024 + (size_t)kStages * (kABytes + COUT * kChunk) + 256 + 2 * COUT * sizeof(float);
+}
+
+// ------------------------------------------------------------------- kernel
+template <bool INT8, int RB, int COUT>
+__global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArgs a) {
+  constexpr int kBBytes = COUT * kChunk;
+  constexpr uint32_t kTmemCols = (2 * COUT < 32) ? 32 : 2 * COUT;
+  constexpr int OPC = RB <= kChunk ? kChunk / RB : 1;   // taps per chunk
+  constexpr int SPO = RB <= kChunk ? RB / 16 : 8;       // 16-byte segments per tap per chunk
+  constexpr int CPT = RB <= kChunk ? 1 : RB / kChunk;   // chunks per tap
+  constexpr int OUT_MAX_B = 2;                          // bytes per output element (max)
+  (void)OUT_MAX_B;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+  uint8_t* sA = smem;
+  uint8_t* sB = sA + kStages * kABytes;
+  uint64_t* bars = (uint64_t*)(sB + kStages * kBBytes);
+  uint32_t* tmem_holder = (uint32_t*)(bars + 2 * kStages + 4);
+  volatile uint32_t* abort_flag = tmem_holder + 1;
+  float* s_scale = (float*)(tmem_holder + 4);
+  float* s_bias = s_scale + COUT;
+
+  const uint32_t bar_full = smem_u32(bars);
+  const uint32_t bar_empty = bar_full + 8 * kStages;
+  const uint32_t bar_tfull = bar_empty + 8 * kStages;
+  const uint32_t bar_tempty = bar_tfull + 16;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar_full + 8 * s, kProdThreads + 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_tfull + 8 * b, 1);
+      mbar_init(bar_tempty + 8 * b, kEpiWarps * 32);
+    }
+    *abort_flag = 0u;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_proxy_async();
+  }
+  if (warp == kMmaWarp) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_holder)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  for (int i = threadIdx.x; i < COUT; i += blockDim.x) {
+    s_scale[i] = a.scale ? a.scale[i] : 1.f;
+    s_bias[i] = a.bias ? a.bias[i] : 0.f;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  const uint32_t n_out = min(*a.n_out_ptr, a.cap);
+  const uint32_t ntiles = (n_out + kTileM - 1) / kTileM;
+  const int kbytes = a.kvol * RB;
+  const int nchunk = (kbytes + kChunk - 1) / kChunk;
+  const int last_ksteps = ((kbytes - (nchunk - 1) * kChunk) + 31) / 32;
+
+  if (warp >= kProdWarp0) {
+    // ------------------------------------------------------------ producers
+    const uint32_t r = threadIdx.x - kProdWarp0 * 32;
+    const uint32_t rsw = r & 7u;
+    const uint32_t a_row_off = (r >> 3) * 1024u + rsw * 128u;
+    uint32_t it = 0;
+    bool alive = true;
+    for (uint32_t tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x) {
+      const uint32_t row = tile * kTileM + r;
+      const bool valid = row < n_out;
+      const int32_t* mrow = a.map + row;
+      int32_t nxt[OPC];
+#pragma unroll
+      for (int o = 0; o < OPC; ++o) {
+        const int k = o;  // chunk 0
+        nxt[o] = (valid && k < a.kvol) ? __ldg(mrow + (size_t)k * a.cap) : -1;
+      }
+      for (int j = 0; j < nchunk; ++j, ++it) {
+        const uint32_t s = it % kStages;
+        const uint32_t ph = (it / kStages) & 1u;
+        if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, a.status, 1u)) {
+          alive = false;
+          break;
+        }
+        if (r == 0) {
+          mbar_expect_tx(bar_full + 8 * s, kBBytes);
+          bulk_g2s(smem_u32(sB + s * kBBytes), a.wpk + (size_t)j * kBBytes, kBBytes,
+                   bar_full + 8 * s);
+        }
+        int32_t cur[OPC];
+#pragma unroll
+        for (int o = 0; o < OPC; ++o) cur[o] = nxt[o];
+        if (j + 1 < nchunk) {
+#pragma unroll
+          for (int o = 0; o < OPC; ++o) {
+            const int k = (RB <= kChunk) ? (j + 1) * OPC + o : (j + 1) / CPT;
+            nxt[o] = (valid && k < a.kvol) ? __ldg(mrow + (size_t)k * a.cap) : -1;
+          }
+        }
+        const uint32_t dst_row = smem_u32(sA + s * kABytes) + a_row_off;
+#pragma unroll
+        for (int o = 0; o < OPC; ++o) {
+          const int32_t src_row = cur[o];
+          const uint8_t* src = a.in + (size_t)(src_row < 0 ? 0 : src_row) * RB +
+                               (RB > kChunk ? (size_t)(j % CPT) * kChunk : 0);
+          const uint32_t nbytes = src_row < 0 ? 0u : 16u;
+#pragma unroll
+          for (int sg = 0; sg < SPO; ++sg) {
+            const uint32_t c = (uint32_t)(o * SPO + sg);
+            cp_async16(dst_row + ((c ^ rsw) << 4), src + sg * 16, nbytes);
+          }
+        }
+        cp_async_commit();
+        if (it >= (uint32_t)kLag) {
+          cp_async_wait<kLag>();
+          fence_proxy_async();
+          mbar_arrive(bar_full + 8 * ((it - kLag) % kStages));
+        }
+      }
+    }
+    cp_async_wait<0>();
+    fence_proxy_async();
+    if (alive) {
+      const uint32_t first = it > (uint32_t)kLag ? it - kLag : 0u;
+      for (uint32_t i = first; i < it; ++i) mbar_arrive(bar_full + 8 * (i % kStages));
+    }
+  } else if (warp == kMmaWarp) {
+    // ------------------------------------------------------------ MMA issue
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc<INT8, COUT>();
+      uint32_t it = 0, tl = 0;
+      bool alive = true;
+      for (uint32_t tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x, ++tl) {
+        const uint32_t buf = tl & 1u;
+        if (!mbar_wait(bar_tempty + 8 * buf, ((tl >> 1) & 1u) ^ 1u, abort_flag, a.status, 2u))
+          break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * COUT;
+        for (int j = 0; j < nchunk; ++j, ++it) {
+          const uint32_t s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1u;
+          if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, a.status, 3u)) {
+            alive = false;
+            break;
+          }
+          tc_fence_after();
+          const uint64_t ad = make_smem_desc(smem_u32(sA + s * kABytes));
+          const uint64_t bd = make_smem_desc(smem_u32(sB + s * kBBytes));
+          const int nk = (j == nchunk - 1) ? last_ksteps : kChunk / 32;
+          for (int ks = 0; ks < nk; ++ks)
+            umma<INT8>(d_tmem, ad + 2u * ks, bd + 2u * ks, idesc, (uint32_t)((j | ks) != 0));
+          tc_commit(bar_empty + 8 * s);
+        }
+        if (alive) tc_commit(bar_tfull + 8 * buf);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------- epilogue
+    const Epilogue ep = a.ep;
+    const int out_b = ep.out_kind == SPCONVB_I8 ? 1 : 2;
+    const int res_b = ep.res_kind == SPCONVB_I8 ? 1 : 2;
+    uint32_t tl = 0;
+    for (uint32_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++tl) {
+      const uint32_t buf = tl & 1u;
+      uint32_t ok = 1u;
+      if (lane == 0)
+        ok = mbar_wait(bar_tfull + 8 * buf, (tl >> 1) & 1u, abort_flag, a.status, 4u) ? 1u : 0u;
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t row = tile * kTileM + warp * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + buf * COUT;
+#pragma unroll 1
+      for (int c0 = 0; c0 < COUT; c0 += 16) {
+        uint32_t v[16];
+        tmem_ld16(taddr + c0, v);
+        tmem_ld_wait();
+        if (c0 + 16 == COUT) {
+          tc_fence_before();
+          mbar_arrive(bar_tempty + 8 * buf);
+        }
+        if (row < n_out) {
+          float rdeq[16];
+          if (ep.has_res) {
+            const uint8_t* rp = a.res + ((size_t)row * COUT + c0) * res_b;
+            if (ep.res_kind == SPCONVB_I8) {
+              const uint4 q = *(const uint4*)rp;
+              const int8_t* qb = (const int8_t*)&q;
+#pragma unroll
+              for (int i = 0; i < 16; ++i) rdeq[i] = __fmul_rn((float)qb[i], ep.res_scale);
+            } else {
+              const uint4 q0 = *(const uint4*)rp;
+              const uint4 q1 = *(const uint4*)(rp + 16);
+              const __half* h0 = (const __half*)&q0;
+              const __half* h1 = (const __half*)&q1;
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                rdeq[i] = __half2float(h0[i]);
+                rdeq[8 + i] = __half2float(h1[i]);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) rdeq[i] = 0.f;
+          }
+          float y[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            float t;
+            if (INT8)
+              t = fmaf((float)(int)v[i], s_scale[c0 + i], s_bias[c0 + i]);
+            else
+              t = __fadd_rn(__uint_as_float(v[i]), s_bias[c0 + i]);
+            y[i] = epilogue_value(t, ep, rdeq[i]);
+          }
+          uint8_t* op = a.out + ((size_t)row * COUT + c0) * out_b;
+          if (ep.out_kind == SPCONVB_I8) {
+            uint32_t w[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              w[i] = ((uint32_t)(uint8_t)(int8_t)(int)y[4 * i + 0]) |
+                     ((uint32_t)(uint8_t)(int8_t)(int)y[4 * i + 1] << 8) |
+                     ((uint32_t)(uint8_t)(int8_t)(int)y[4 * i + 2] << 16) |
+                     ((uint32_t)(uint8_t)(int8_t)(int)y[4 * i + 3] << 24);
+            }
+            *(uint4*)op = make_uint4(w[0], w[1], w[2], w[3]);
+          } else {
+            uint32_t w[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              __half2 h = __floats2half2_rn(y[2 * i], y[2 * i + 1]);
+              w[i] = *(uint32_t*)&h;
+            }
+            *(uint4*)op = make_uint4(w[0], w[1], w[2], w[3]);
+            *(uint4*)(op + 16) = make_uint4(w[4], w[5], w[6], w[7]);
+          }
+        }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // give copies already issued a bounded time to land before the CTA exits
+    const unsigned long long t0 = global_ns();
+    while (global_ns() - t0 < 50000ull) {
+    }
+    __syncthreads();
+  }
+  if (warp == kMmaWarp) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(kTmemCols)
+                 : "memory");
+  }
+}
+
+template <bool INT8, int RB, int COUT>
+int launch_one(const UmmaArgs& args, uint32_t launch_rows, cudaStream_t st) {
+  static bool attr_done[64] = {};
+  int dev = 0;
+  SPCONVB_CUDA_TRY(cudaGetDevice(&dev));
+  constexpr size_t smem = umma_smem_bytes<COUT>();
+  if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+    SPCONVB_CUDA_TRY(cudaFuncSetAttribute(conv_umma_kernel<INT8, RB, COUT>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)smem));
+    if (dev >= 0 && dev < 64) attr_done[dev] = true;
+  }
+  uint32_t tiles = (launch_rows + kTileM - 1) / kTileM;
+  int grid = (int)(tiles < (uint32_t)kSmCount ? (tiles ? tiles : 1u) : (uint32_t)kSmCount);
+  conv_umma_kernel<INT8, RB, COUT><<<grid, kCtaThreads, smem, st>>>(args);
+  SPCONVB_LAUNCH_CHECK();
+  return SPCONVB_OK;
+}
+
+template <bool INT8, int RB>
+int launch_cout(int cout, const UmmaArgs& args, uint32_t launch_rows, cudaStream_t st) {
+  switch (cout) {
+    case 16: return launch_one<INT8, RB, 16>(args, launch_rows, st);
+    case 32: return launch_one<INT8, RB, 32>(args, launch_rows, st);
+    case 64: return launch_one<INT8, RB, 64>(args, launch_rows, st);
+    case 128: return launch_one<INT8, RB, 128>(args, launch_rows, st);
+  }
+  return SPCONVB_E_UNSUPPORTED;
+}
+
+template <bool INT8>
+int launch_rb(int rb, int cout, const UmmaArgs& args, uint32_t launch_rows, cudaStream_t st) {
+  switch (rb) {
+    case 16: return launch_cout<INT8, 16>(cout, args, launch_rows, st);
+    case 32: return launch_cout<INT8, 32>(cout, args, launch_rows, st);
+    case 64: return launch_cout<INT8, 64>(cout, args, launch_rows, st);
+    case 128: return launch_cout<INT8, 128>(cout, args, launch_rows, st);
+    case 256: return launch_cout<INT8, 256>(cout, args, launch_rows, st);
+  }
+  return SPCONVB_E_UNSUPPORTED;
+}
+
+inline int row_bytes(int compute, int cin) { return cin * (compute == SPCONVB_I8 ? 1 : 2); }
+
+}  // namespace
+
+bool conv_umma_supported(int compute, int cin, int cout) {
+  const int rb = row_bytes(compute, cin);
+  const bool rb_ok = rb == 16 || rb == 32 || rb == 64 || rb == 128 || (rb == 256);
+  const bool co_ok = cout == 16 || cout == 32 || cout == 64 || cout == 128;
+  return (compute == SPCONVB_I8 || compute == SPCONVB_F16) && rb_ok && co_ok;
+}
+
+size_t conv_umma_packed_bytes(int compute, int cin, int cout, int kvol) {
+  const size_t kbytes = (size_t)kvol * row_bytes(compute, cin);
+  const size_t nchunk = (kbytes + kChunk - 1) / kChunk;
+  return nchunk * (size_t)cout * kChunk;
+}
+
+// Host: lay the weights out as the shared-memory image of each 128-byte K chunk
+// (row n of a chunk = bytes [j*128, j*128+128) of W[n] flattened over (tap, cin),
+// zero padded; 16-byte segment c of row n stored at segment c ^ (n % 8)).
+int conv_umma_pack(int compute, int cin, int cout, int kvol, const void* w, void* dst) {
+  if (!conv_umma_supported(compute, cin, cout) || !w || !dst || kvol < 1) return SPCONVB_E_ARG;
+  const size_t rowlen = (size_t)kvol * row_bytes(compute, cin);
+  const size_t nchunk = (rowlen + kChunk - 1) / kChunk;
+  const uint8_t* src = (const uint8_t*)w;
+  uint8_t* out = (uint8_t*)dst;
+  for (size_t j = 0; j < nchunk; ++j)
+    for (int n = 0; n < cout; ++n)
+      for (int c = 0; c < 8; ++c) {
+        uint8_t* d = out + j * (size_t)cout * kChunk + (size_t)(n / 8) * 1024 + (n % 8) * 128 +
+                     ((c ^ (n % 8)) << 4);
+        const size_t kb = j * kChunk + (size_t)c * 16;
+        for (int b = 0; b < 16; ++b)
+          d[b] = (kb + b < rowlen) ? src[(size_t)n * rowlen + kb + b] : (uint8_t)0;
+      }
+  return SPCONVB_OK;
+}
+
+int conv_umma_launch(const spconvb_conv_params& p, const void* in, const int32_t* map,
+                     uint32_t cap, const uint32_t* n_out_ptr, uint32_t launch_rows,
+                     const void* w_packed, const float* scale, const float* bias, void* out,
+                     uint32_t* status, cudaStream_t st) {
+  if (!w_packed) return SPCONVB_E_ARG;
+  if (p.compute == SPCONVB_I8 && !scale) return SPCONVB_E_ARG;
+  if (((uintptr_t)in | (uintptr_t)out | (uintptr_t)w_packed | (uintptr_t)p.res) & 15u)
+    return SPCONVB_E_ARG;
+  UmmaArgs a;
+  a.in = (const uint8_t*)in;
+  a.map = map;
+  a.cap = cap;
+  a.n_out_ptr = n_out_ptr;
+  a.wpk = (const uint8_t*)w_packed;
+  a.scale = p.compute == SPCONVB_I8 ? scale : nullptr;
+  a.bias = bias;
+  a.res = (const uint8_t*)p.res;
+  a.out = (uint8_t*)out;
+  a.status = status;
+  a.kvol = p.kvol;
+  a.ep = make_epilogue(p);
+  const int rb = row_bytes(p.compute, p.cin);
+  if (p.compute == SPCONVB_I8) return launch_rb<true>(rb, p.cout, a, launch_rows, st);
+  return launch_rb<false>(rb, p.cout, a, launch_rows, st);
+}
+
+}  // namespace spconvb

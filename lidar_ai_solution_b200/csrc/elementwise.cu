@@ -1,0 +1,269 @@
+// HBM-bound helpers around the convolutions: Add / Add&ReLU / ReLU, precision
+// and channel-padding conversion, and the sparse -> dense BEV scatter.
+#include "common.cuh"
+
+namespace spconvb {
+
+__device__ __forceinline__ float load_deq(const void* p, int kind, float scale, size_t i) {
+  if (kind == SPCONVB_I8) return __fmul_rn((float)((const int8_t*)p)[i], scale);
+  return __half2float(((const __half*)p)[i]);
+}
+
+__device__ __forceinline__ void store_q(void* p, int kind, float inv_scale, size_t i, float y) {
+  if (kind == SPCONVB_I8)
+    ((int8_t*)p)[i] = (int8_t)sat8(__fmul_rn(y, inv_scale));
+  else
+    ((__half*)p)[i] = __float2half_rn(y);
+}
+
+// 16 consecutive elements per thread, 16-byte loads and stores.
+template <int AK, int BK, int OK>
+__global__ void add_vec_kernel(const void* __restrict__ a, float a_scale,
+                               const void* __restrict__ b, float b_scale, int channels,
+                               const uint32_t* n_ptr, int relu, float inv_out_scale,
+                               void* __restrict__ out) {
+  const size_t groups = (size_t)(*n_ptr) * channels / 16;
+  for (size_t gidx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; gidx < groups;
+       gidx += (size_t)gridDim.x * blockDim.x) {
+    float x[16], y[16];
+    if (AK == SPCONVB_I8) {
+      uint4 q = ((const uint4*)a)[gidx];
+      const int8_t* s = (const int8_t*)&q;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) x[i] = __fmul_rn((float)s[i], a_scale);
+    } else {
+      uint4 q0 = ((const uint4*)a)[2 * gidx], q1 = ((const uint4*)a)[2 * gidx + 1];
+      const __half* h0 = (const __half*)&q0;
+      const __half* h1 = (const __half*)&q1;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { x[i] = __half2float(h0[i]); x[8 + i] = __half2float(h1[i]); }
+    }
+    if (BK == SPCONVB_I8) {
+      uint4 q = ((const uint4*)b)[gidx];
+      const int8_t* s = (const int8_t*)&q;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) y[i] = __fmul_rn((float)s[i], b_scale);
+    } else {
+      uint4 q0 = ((const uint4*)b)[2 * gidx], q1 = ((const uint4*)b)[2 * gidx + 1];
+      const __half* h0 = (const __half*)&q0;
+      const __half* h1 = (const __half*)&q1;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { y[i] = __half2float(h0[i]); y[8 + i] = __half2float(h1[i]); }
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      x[i] = __fadd_rn(x[i], y[i]);
+      if (relu) x[i] = fmaxf(x[i], 0.f);
+    }
+    if (OK == SPCONVB_I8) {
+      uint32_t w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        w[i] = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          w[i] |= (uint32_t)(uint8_t)(int8_t)sat8(__fmul_rn(x[4 * i + j], inv_out_scale))
+                  << (8 * j);
+      }
+      ((uint4*)out)[gidx] = make_uint4(w[0], w[1], w[2], w[3]);
+    } else {
+      uint32_t w[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        __half2 h = __floats2half2_rn(x[2 * i], x[2 * i + 1]);
+        w[i] = *(uint32_t*)&h;
+      }
+      ((uint4*)out)[2 * gidx] = make_uint4(w[0], w[1], w[2], w[3]);
+      ((uint4*)out)[2 * gidx + 1] = make_uint4(w[4], w[5], w[6], w[7]);
+    }
+  }
+}
+
+__global__ void add_scalar_kernel(const void* a, int a_kind, float a_scale, const void* b,
+                                  int b_kind, float b_scale, int channels, const uint32_t* n_ptr,
+                                  int relu, int out_kind, float inv_out_scale, void* out) {
+  const size_t total = (size_t)(*n_ptr) * channels;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (size_t)gridDim.x * blockDim.x) {
+    float y = __fadd_rn(load_deq(a, a_kind, a_scale, i), load_deq(b, b_kind, b_scale, i));
+    if (relu) y = fmaxf(y, 0.f);
+    store_q(out, out_kind, inv_out_scale, i, y);
+  }
+}
+
+__global__ void relu_kernel(const void* x, int kind, int channels, const uint32_t* n_ptr,
+                            void* out) {
+  const size_t total = (size_t)(*n_ptr) * channels;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (size_t)gridDim.x * blockDim.x) {
+    if (kind == SPCONVB_I8) {
+      int8_t v = ((const int8_t*)x)[i];
+      ((int8_t*)out)[i] = v > 0 ? v : (int8_t)0;
+    } else {
+      uint16_t v = ((const uint16_t*)x)[i];
+      // negative non-NaN values (including -0) become +0
+      ((uint16_t*)out)[i] = ((v & 0x8000u) && ((v & 0x7fffu) <= 0x7c00u)) ? (uint16_t)0 : v;
+    }
+  }
+}
+
+__global__ void convert_kernel(const void* x, int in_kind, int cin, int out_kind, int cout,
+                               float s, const uint32_t* n_ptr, void* out) {
+  const size_t total = (size_t)(*n_ptr) * cout;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (size_t)gridDim.x * blockDim.x) {
+    const size_t row = i / cout;
+    const int c = (int)(i % cout);
+    if (c >= cin) {
+      if (out_kind == SPCONVB_I8) ((int8_t*)out)[i] = 0;
+      else ((uint16_t*)out)[i] = 0;
+      continue;
+    }
+    const size_t j = row * cin + c;
+    if (in_kind == out_kind) {
+      if (out_kind == SPCONVB_I8) ((int8_t*)out)[i] = ((const int8_t*)x)[j];
+      else ((uint16_t*)out)[i] = ((const uint16_t*)x)[j];
+    } else if (out_kind == SPCONVB_I8) {
+      ((int8_t*)out)[i] = (int8_t)sat8(__fmul_rn(__half2float(((const __half*)x)[j]), s));
+    } else {
+      ((__half*)out)[i] = __float2half_rn(__fmul_rn((float)((const int8_t*)x)[j], s));
+    }
+  }
+}
+
+// 32 rows per block: rows are read coalesced into shared memory, then written
+// channel by channel so that neighbouring rows (neighbouring cells when the
+// rows are in canonical order) share write sectors.
+__global__ void scatter_dense_kernel(const void* __restrict__ feat, int in_kind, float in_scale,
+                                     const int4* __restrict__ coords, const uint32_t* n_ptr,
+                                     int channels, Grid3 g, int p0, int p1, int p2,
+                                     __half* __restrict__ out) {
+  extern __shared__ __half tile[];  // [channels][33]
+  __shared__ long long s_cell[32];
+  const uint32_t n = *n_ptr;
+  const int gp[3] = {g.g[p0], g.g[p1], g.g[p2]};
+  const size_t vol = (size_t)gp[0] * gp[1] * gp[2];
+  for (uint32_t row0 = blockIdx.x * 32; row0 < n; row0 += gridDim.x * 32) {
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      long long cell = -1;
+      uint32_t row = row0 + threadIdx.x;
+      if (row < n) {
+        int4 c = coords[row];
+        const int sp[3] = {c.y, c.z, c.w};
+        const int s0 = sp[p0], s1 = sp[p1], s2 = sp[p2];
+        if ((unsigned)c.x < (unsigned)g.batch && (unsigned)s0 < (unsigned)gp[0] &&
+            (unsigned)s1 < (unsigned)gp[1] && (unsigned)s2 < (unsigned)gp[2])
+          cell = (long long)c.x * channels * (long long)vol + ((long long)s0 * gp[1] + s1) * gp[2] + s2;
+      }
+      s_cell[threadIdx.x] = cell;
+    }
+    for (int i = threadIdx.x; i < 32 * channels; i += blockDim.x) {
+      const int r = i / channels, ch = i % channels;
+      const uint32_t row = row0 + r;
+      __half v = __float2half(0.f);
+      if (row < n) {
+        const size_t j = (size_t)row * channels + ch;
+        v = in_kind == SPCONVB_I8
+                ? __float2half_rn(__fmul_rn((float)((const int8_t*)feat)[j], in_scale))
+                : ((const __half*)feat)[j];
+      }
+      tile[ch * 33 + r] = v;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 32 * channels; i += blockDim.x) {
+      const int ch = i >> 5, r = i & 31;
+      const long long cell = s_cell[r];
+      if (cell >= 0) out[cell + (long long)ch * (long long)vol] = tile[ch * 33 + r];
+    }
+  }
+}
+
+static inline uint32_t clamp_u32(size_t v) { return v > 0xffffffffull ? 0xffffffffu : (uint32_t)v; }
+
+}  // namespace spconvb
+
+using namespace spconvb;
+
+extern "C" {
+
+int spconvb_add(const void* a, int32_t a_kind, float a_scale, const void* b, int32_t b_kind,
+                float b_scale, int32_t channels, const uint32_t* n_ptr, uint32_t launch_rows,
+                int32_t relu, int32_t out_kind, float inv_out_scale, void* out, void* stream) {
+  if (!a || !b || !out || !n_ptr || channels < 1 || launch_rows < 1) return SPCONVB_E_ARG;
+  cudaStream_t st = (cudaStream_t)stream;
+  const bool aligned = !(((uintptr_t)a | (uintptr_t)b | (uintptr_t)out) & 15u);
+  if (channels % 16 == 0 && aligned) {
+    const uint32_t groups = (uint32_t)((size_t)launch_rows * channels / 16);
+    const int blocks = blocks_for(groups, 256);
+#define SPCONVB_ADD_CASE(AK, BK, OK)                                                        \
+  if (a_kind == AK && b_kind == BK && out_kind == OK) {                                     \
+    add_vec_kernel<AK, BK, OK><<<blocks, 256, 0, st>>>(a, a_scale, b, b_scale, channels,    \
+                                                       n_ptr, relu, inv_out_scale, out);    \
+    SPCONVB_LAUNCH_CHECK();                                                                 \
+    return SPCONVB_OK;                                                                      \
+  }
+    SPCONVB_ADD_CASE(0, 0, 0) SPCONVB_ADD_CASE(0, 0, 1) SPCONVB_ADD_CASE(0, 1, 0)
+    SPCONVB_ADD_CASE(0, 1, 1) SPCONVB_ADD_CASE(1, 0, 0) SPCONVB_ADD_CASE(1, 0, 1)
+    SPCONVB_ADD_CASE(1, 1, 0) SPCONVB_ADD_CASE(1, 1, 1)
+#undef SPCONVB_ADD_CASE
+    return SPCONVB_E_ARG;
+  }
+  const uint32_t work = clamp_u32((size_t)launch_rows * channels);
+  add_scalar_kernel<<<blocks_for(work, 256), 256, 0, st>>>(a, a_kind, a_scale, b, b_kind, b_scale,
+                                                           channels, n_ptr, relu, out_kind,
+                                                           inv_out_scale, out);
+  SPCONVB_LAUNCH_CHECK();
+  return SPCONVB_OK;
+}
+
+int spconvb_relu(const void* x, int32_t kind, int32_t channels, const uint32_t* n_ptr,
+                 uint32_t launch_rows, void* out, void* stream) {
+  if (!x || !out || !n_ptr || channels < 1 || launch_rows < 1) return SPCONVB_E_ARG;
+  const uint32_t work = clamp_u32((size_t)launch_rows * channels);
+  relu_kernel<<<blocks_for(work, 256), 256, 0, (cudaStream_t)stream>>>(x, kind, channels, n_ptr,
+                                                                       out);
+  SPCONVB_LAUNCH_CHECK();
+  return SPCONVB_OK;
+}
+
+int spconvb_convert(const void* x, int32_t in_kind, int32_t cin, int32_t out_kind,
+                    int32_t cout_pad, float scale_or_inv, const uint32_t* n_ptr,
+                    uint32_t launch_rows, void* out, void* stream) {
+  if (!x || !out || !n_ptr || cin < 1 || cout_pad < cin || launch_rows < 1) return SPCONVB_E_ARG;
+  const uint32_t work = clamp_u32((size_t)launch_rows * cout_pad);
+  convert_kernel<<<blocks_for(work, 256), 256, 0, (cudaStream_t)stream>>>(
+      x, in_kind, cin, out_kind, cout_pad, scale_or_inv, n_ptr, out);
+  SPCONVB_LAUNCH_CHECK();
+  return SPCONVB_OK;
+}
+
+int spconvb_scatter_dense(const void* feat, int32_t in_kind, float in_scale,
+                          const int32_t* coords, const uint32_t* n_ptr, uint32_t launch_rows,
+                          int32_t channels, int32_t batch, const int32_t grid[3],
+                          const int32_t perm[3], void* out, void* stream) {
+  if (!feat || !coords || !n_ptr || !grid || !out || channels < 1 || channels > 1024 ||
+      batch < 1 || launch_rows < 1)
+    return SPCONVB_E_ARG;
+  int p[3] = {0, 1, 2};
+  if (perm) {
+    p[0] = perm[0]; p[1] = perm[1]; p[2] = perm[2];
+    if ((1 << p[0] | 1 << p[1] | 1 << p[2]) != 7) return SPCONVB_E_ARG;
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  Grid3 g;
+  g.g[0] = grid[0]; g.g[1] = grid[1]; g.g[2] = grid[2];
+  g.batch = batch;
+  const size_t bytes = sizeof(__half) * (size_t)batch * channels * grid[0] * grid[1] * grid[2];
+  SPCONVB_CUDA_TRY(cudaMemsetAsync(out, 0, bytes, st));
+  size_t want_blocks = ((size_t)launch_rows + 31) / 32;
+  if (want_blocks > (size_t)kSmCount * 16) want_blocks = (size_t)kSmCount * 16;
+  const int blocks = (int)want_blocks;
+  scatter_dense_kernel<<<blocks, 256, sizeof(__half) * 33 * channels, st>>>(
+      feat, in_kind, in_scale, (const int4*)coords, n_ptr, channels, g, p[0], p[1], p[2],
+      (__half*)out);
+  SPCONVB_LAUNCH_CHECK();
+  return SPCONVB_OK;
+}
+
+}  // extern "C"

@@ -27,8 +27,17 @@ def make_coords(n: int, grid_zyx=CENTERPOINT_GRID_ZYX, seed: int = 0) -> np.ndar
     rng = np.random.default_rng(seed)
     if n <= 0:
         return np.zeros((0, 4), np.int32)
-    if n > gz * gy * gx // 4:
-        raise ValueError("scene denser than a quarter of the grid")
+    cells = gz * gy * gx
+    if n > cells:
+        raise ValueError("more voxels than grid cells")
+    if n > cells // 8:
+        # too dense for the lidar law (tiny test grids): uniform without replacement
+        keys = rng.permutation(cells)[:n].astype(np.int64)
+        out = np.zeros((n, 4), np.int32)
+        out[:, 3] = keys % gx
+        out[:, 2] = (keys // gx) % gy
+        out[:, 1] = keys // (gx * gy)
+        return out
 
     n_boxes = max(1, int(round(50 * n / 20000)))
     bz, by, bx = min(4, gz), min(4, gy), min(8, gx)

@@ -431,9 +431,15 @@ int orc_voxelize(const void* points, int points_kind, int n, int nfeat, const fl
     if (p[0] < range[0] || p[0] >= range[3] || p[1] < range[1] || p[1] >= range[4] ||
         p[2] < range[2] || p[2] >= range[5])
       continue;
-    unsigned vx = (unsigned)floorf((p[0] - range[0]) / vsize[0]);
-    unsigned vy = (unsigned)floorf((p[1] - range[1]) / vsize[1]);
-    unsigned vz = (unsigned)floorf((p[2] - range[2]) / vsize[2]);
+    int ivx = (int)floorf((p[0] - range[0]) / vsize[0]);
+    int ivy = (int)floorf((p[1] - range[1]) / vsize[1]);
+    int ivz = (int)floorf((p[2] - range[2]) / vsize[2]);
+    /* a quotient that rounds up to the grid size is outside (the BEVFusion copy
+     * of the kernel checks this, lidar-voxelization.cu:86-93) */
+    if (ivx < 0 || ivx >= gridxyz[0] || ivy < 0 || ivy >= gridxyz[1] || ivz < 0 ||
+        ivz >= gridxyz[2])
+      continue;
+    unsigned vx = (unsigned)ivx, vy = (unsigned)ivy, vz = (unsigned)ivz;
     uint32_t key = (vz * (uint32_t)gridxyz[1] + vy) * (uint32_t)gridxyz[0] + vx;
     uint64_t h = key;
     h ^= h >> 16; h *= 0x85ebca6bull; h ^= h >> 13; h *= 0xc2b2ae35ull; h ^= h >> 16;

@@ -1,0 +1,380 @@
+"""Kernel-level parity: every CUDA entry point of the C ABI against the CPU oracle
+on the same seeded inputs.  Integer and index results must be identical; fp16
+tensor-core results are within 1e-2 relative (stated per test)."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+
+from lidar_ai_solution_b200 import scenes  # noqa: E402
+from oracle import oracle as orc  # noqa: E402
+from tests.helpers import int8_problem, kaiming  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+STAGES = [((3, 3, 3), (2, 2, 2), (1, 1, 1)), ((3, 3, 3), (2, 2, 2), (1, 1, 1)),
+          ((3, 3, 3), (2, 2, 2), (0, 1, 1)), ((3, 1, 1), (2, 1, 1), (0, 0, 0))]
+
+
+def _ops():
+    from lidar_ai_solution_b200 import ops
+    return ops
+
+
+def _dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def _status_ok(status):
+    s = status.cpu().numpy()
+    assert s[0] == 0, "device status %s" % s
+
+
+# ------------------------------------------------------------------ rulebooks
+@pytest.mark.parametrize("n,grid,seed", [(20000, (41, 180, 180), 0), (20000, (41, 180, 180), 3),
+                                         (120000, (41, 1440, 1440), 1), (1, (41, 180, 180), 0),
+                                         (129, (5, 7, 9), 2)])
+def test_subm_map_bit_exact(n, grid, seed):
+    ops = _ops()
+    coords = scenes.make_coords(n, grid, seed)
+    ref, pairs = orc.subm_map(coords, grid)
+    dc, n_ptr, st = _dev(coords), ops.device_count(n), ops.new_status()
+    table = ops.hash_build(dc, n_ptr, grid, status=st)
+    m = ops.subm_map(dc, n_ptr, grid, table, status=st)
+    torch.cuda.synchronize()
+    _status_ok(st)
+    got = m.cpu().numpy()
+    assert np.array_equal(got, ref)
+    assert int((got >= 0).sum()) == pairs
+
+
+def test_subm_map_capacity_larger_than_rows():
+    """Buffers sized for a bound, row count on the device (the DDS calling pattern)."""
+    ops = _ops()
+    grid, n, cap = (41, 180, 180), 5000, 8192
+    coords = scenes.make_coords(n, grid, 5)
+    padded = np.full((cap, 4), 7, np.int32)
+    padded[:n] = coords
+    ref, _ = orc.subm_map(coords, grid, cap=cap)
+    dc, n_ptr, st = _dev(padded), ops.device_count(n), ops.new_status()
+    table = ops.hash_build(dc, n_ptr, grid, status=st)
+    m = torch.full((27, cap), -1, dtype=torch.int32, device="cuda")
+    from lidar_ai_solution_b200 import cabi
+    cabi.check(cabi.lib().spconvb_subm_map(dc.data_ptr(), n_ptr.data_ptr(), cap, 2048,
+                                           cabi.i3(grid), 1, cabi.i3((3, 3, 3)),
+                                           cabi.i3((1, 1, 1)), table.data_ptr(), table.numel(),
+                                           m.data_ptr(), st.data_ptr(),
+                                           torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    _status_ok(st)
+    assert np.array_equal(m.cpu().numpy(), ref)
+
+
+def test_hash_reports_duplicates_and_range():
+    ops = _ops()
+    grid = (8, 8, 8)
+    coords = np.array([[0, 1, 1, 1], [0, 1, 1, 1], [0, 9, 0, 0]], np.int32)
+    st = ops.new_status()
+    ops.hash_build(_dev(coords), ops.device_count(3), grid, status=st)
+    torch.cuda.synchronize()
+    from lidar_ai_solution_b200 import cabi
+    bits = int(st.cpu().numpy()[0])
+    assert bits & cabi.ST_DUPLICATE and bits & cabi.ST_COORD_RANGE
+
+
+def _chain(coords, grid):
+    ops = _ops()
+    dc, n_ptr, st = _dev(coords), ops.device_count(len(coords)), ops.new_status()
+    table = ops.hash_build(dc, n_ptr, grid, status=st)
+    out = []
+    for k, s, p in STAGES:
+        m = ops.subm_map(dc, n_ptr, grid, table, status=st)
+        oc, n_out, dm, otab, og = ops.down_map(dc, n_ptr, grid, table, k, s, p, status=st)
+        torch.cuda.synchronize()
+        _status_ok(st)
+        out.append((dc, n_ptr, list(grid), m, oc, n_out, dm, og))
+        dc, n_ptr, table, grid = oc, n_out, otab, og
+    return out
+
+
+def test_stage_chain_matches_oracle_and_fixture_counts(golden_dir):
+    """The reference's 79 745-voxel CenterPoint frame through the backbone's four
+    resolutions: maps and output coordinates identical to the oracle, counts equal
+    to the committed golden counts."""
+    z = np.load(os.path.join(golden_dir, "fixture_coords.npz"))
+    counts = json.load(open(os.path.join(golden_dir, "fixture_counts.json")))
+    for name, key in (("centerpoint", "centerpoint_zyx"), ("bevfusion", "bevfusion_zyx")):
+        zyx = z[key].astype(np.int32)
+        coords = np.concatenate([np.zeros((len(zyx), 1), np.int32), zyx], 1)
+        grid = [41, 1440, 1440]
+        c_ref = coords
+        for stage, (dc, n_ptr, g, m, oc, n_out, dm, og) in enumerate(_chain(coords, grid)):
+            n = int(n_ptr.item())
+            ref_m, pairs = orc.subm_map(c_ref, g)
+            assert np.array_equal(m.cpu().numpy()[:, :n], ref_m)
+            k, s, p = STAGES[stage]
+            roc, rdm, dpairs, rog, rn = orc.down_map(c_ref, g, k, s, p, cap=oc.shape[0])
+            assert int(n_out.item()) == rn and og == rog
+            assert np.array_equal(oc.cpu().numpy()[:rn], roc)
+            assert np.array_equal(dm.cpu().numpy()[:, :rn], rdm[:, :rn])
+            gold = counts[name][stage]
+            assert (n, pairs, rn, dpairs) == (gold["n"], gold["subm_pairs"], gold["down_n"],
+                                              gold["down_pairs"])
+            c_ref = roc
+
+
+def test_down_map_overflow_sets_status():
+    ops = _ops()
+    from lidar_ai_solution_b200 import cabi
+    grid = (9, 33, 33)
+    coords = scenes.make_coords(600, grid, 4)
+    dc, n_ptr, st = _dev(coords), ops.device_count(600), ops.new_status()
+    table = ops.hash_build(dc, n_ptr, grid, status=st)
+    oc, n_out, dm, _, _ = ops.down_map(dc, n_ptr, grid, table, (3, 3, 3), (2, 2, 2), (1, 1, 1),
+                                       cap_out=64, status=st)
+    torch.cuda.synchronize()
+    assert int(n_out.item()) == 64
+    assert int(st.cpu().numpy()[0]) & cabi.ST_OVERFLOW
+    roc, rdm, _, _, rn = orc.down_map(coords, grid, (3, 3, 3), (2, 2, 2), (1, 1, 1), cap=64)
+    assert rn > 64 and np.array_equal(oc.cpu().numpy(), roc)
+    assert np.array_equal(dm.cpu().numpy(), rdm)
+
+
+# --------------------------------------------------------------- convolutions
+def _int8_layer(n, c_in, c_out, seed, simt, out_kind, grid=(41, 180, 180)):
+    ops = _ops()
+    pb = int8_problem(n, c_in, c_out, grid, seed)
+    m_ref, _ = orc.subm_map(pb["coords"], grid)
+    y32 = orc.conv_i8(pb["xq"], m_ref, n, pb["wq"], pb["scale"], pb["bias"], orc.ACT_RELU,
+                      orc.KIND_F32)
+    inv_out = np.float32(127.0) / np.float32(max(float(np.abs(y32).max()), 1e-6))
+    ref = orc.conv_i8(pb["xq"], m_ref, n, pb["wq"], pb["scale"], pb["bias"], orc.ACT_RELU,
+                      out_kind, float(inv_out))
+    n_ptr, st = ops.device_count(n), ops.new_status()
+    wts = ops.ConvWeights(pb["wq"], ops.I8, pb["scale"], pb["bias"])
+    out = ops.conv_forward(_dev(pb["xq"]), _dev(m_ref), n_ptr, wts, act=ops.ACT_RELU,
+                           out_kind=out_kind, inv_out_scale=float(inv_out), force_simt=simt,
+                           status=st)
+    torch.cuda.synchronize()
+    _status_ok(st)
+    return out.cpu().numpy(), ref
+
+
+@pytest.mark.parametrize("c", [16, 32, 64, 128])
+@pytest.mark.parametrize("simt", [False, True])
+def test_conv_int8_bit_exact(c, simt):
+    """int8 x int8 -> int32 is exact, the epilogue is defined operation by operation,
+    so the requantised int8 output must be identical (tolerance 0 LSB)."""
+    got, ref = _int8_layer(3000 if simt else 10000, c, c, seed=c, simt=simt, out_kind=orc.KIND_I8)
+    assert got.dtype == np.int8 and np.array_equal(got, ref)
+
+
+@pytest.mark.parametrize("cin,cout", [(16, 32), (32, 64), (64, 128), (128, 16)])
+def test_conv_int8_mixed_channels_fp16_out(cin, cout):
+    got, ref = _int8_layer(4097, cin, cout, seed=cin + cout, simt=False, out_kind=orc.KIND_F16)
+    assert np.array_equal(got.view(np.uint16), ref.view(np.uint16))
+
+
+@pytest.mark.parametrize("n", [0, 1, 127, 128, 129, 257])
+def test_conv_int8_ragged_row_counts(n):
+    if n == 0:
+        ops = _ops()
+        wts = ops.ConvWeights(np.zeros((16, 27, 16), np.int8), ops.I8, np.ones(16, np.float32),
+                              np.zeros(16, np.float32))
+        st = ops.new_status()
+        out = ops.conv_forward(torch.zeros((1, 16), dtype=torch.int8, device="cuda"),
+                               torch.full((27, 1), -1, dtype=torch.int32, device="cuda"),
+                               ops.device_count(0), wts, out_kind=ops.I8, status=st)
+        torch.cuda.synchronize()
+        _status_ok(st)
+        assert out.shape == (1, 16)
+        return
+    got, ref = _int8_layer(n, 32, 32, seed=n, simt=False, out_kind=orc.KIND_I8, grid=(5, 9, 11))
+    assert np.array_equal(got, ref)
+
+
+def _f16_problem(n, cin, cout, seed, grid=(41, 180, 180), kvol=27):
+    rng = np.random.default_rng(seed)
+    coords = scenes.make_coords(n, grid, seed)
+    x = rng.standard_normal((n, cin)).astype(np.float16)
+    w = kaiming(rng, cout, kvol, cin).astype(np.float16)
+    bias = (rng.standard_normal(cout) * 0.1).astype(np.float32)
+    return coords, x, w, bias
+
+
+@pytest.mark.parametrize("c", [16, 32, 64, 128])
+def test_conv_fp16_tensor_core(c):
+    """fp16 operands, fp32 accumulation in a different order than the oracle:
+    tolerance 1e-2 relative to the layer's output magnitude."""
+    ops = _ops()
+    grid, n = (41, 180, 180), 8000
+    coords, x, w, bias = _f16_problem(n, c, c, seed=c + 1)
+    m_ref, _ = orc.subm_map(coords, grid)
+    ref = orc.conv_f16(x, m_ref, n, w, bias, orc.ACT_RELU, orc.KIND_F16).astype(np.float32)
+    wts = ops.ConvWeights(w, ops.F16, None, bias)
+    st = ops.new_status()
+    out = ops.conv_forward(_dev(x), _dev(m_ref), ops.device_count(n), wts, act=ops.ACT_RELU,
+                           out_kind=ops.F16, status=st)
+    torch.cuda.synchronize()
+    _status_ok(st)
+    got = out.cpu().numpy().astype(np.float32)
+    tol = 1e-2 * max(float(np.abs(ref).max()), 1e-6)
+    assert float(np.abs(got - ref).max()) <= tol
+
+
+def test_conv_fp16_cuda_core_bit_exact_and_first_layer_padding():
+    """Cin = 5 padded to 8 (the backbone's first layer) on the tensor-core kernel vs the
+    CUDA-core kernel on the unpadded data; the CUDA-core kernel equals the oracle bit for bit."""
+    ops = _ops()
+    grid, n = (41, 180, 180), 6000
+    coords, x, w, bias = _f16_problem(n, 5, 16, seed=11)
+    m_ref, _ = orc.subm_map(coords, grid)
+    ref = orc.conv_f16(x, m_ref, n, w, bias, orc.ACT_RELU, orc.KIND_F16)
+    n_ptr, md = ops.device_count(n), _dev(m_ref)
+    simt = ops.conv_forward(_dev(x), md, n_ptr, ops.ConvWeights(w, ops.F16, None, bias),
+                            act=ops.ACT_RELU, out_kind=ops.F16, force_simt=True)
+    assert np.array_equal(simt.cpu().numpy().view(np.uint16), ref.view(np.uint16))
+    wp = np.zeros((16, 27, 8), np.float16)
+    wp[:, :, :5] = w
+    xp = ops.convert(_dev(x), ops.F16, 8, 1.0, n_ptr)
+    st = ops.new_status()
+    tc = ops.conv_forward(xp, md, n_ptr, ops.ConvWeights(wp, ops.F16, None, bias),
+                          act=ops.ACT_RELU, out_kind=ops.F16, status=st)
+    torch.cuda.synchronize()
+    _status_ok(st)
+    r32 = ref.astype(np.float32)
+    assert float(np.abs(tc.cpu().numpy().astype(np.float32) - r32).max()) <= 1e-2 * np.abs(r32).max()
+
+
+@pytest.mark.parametrize("simt", [False, True])
+def test_conv_int8_fused_residual_equals_conv_then_add(simt):
+    """Fused conv + Add&ReLU epilogue == oracle conv (stored int8) followed by oracle add."""
+    ops = _ops()
+    grid, n, c = (41, 180, 180), 5000, 64
+    pb = int8_problem(n, c, c, grid, seed=21)
+    m_ref, _ = orc.subm_map(pb["coords"], grid)
+    rng = np.random.default_rng(5)
+    res = rng.integers(-128, 128, (n, c)).astype(np.int8)
+    res_scale, mid_dr, out_dr = 0.031, 3.0, 4.5
+    mid = orc.conv_i8(pb["xq"], m_ref, n, pb["wq"], pb["scale"], pb["bias"], orc.ACT_NONE,
+                      orc.KIND_I8, float(np.float32(127.0) / np.float32(mid_dr)))
+    ref = orc.add(mid, float(np.float32(mid_dr) / np.float32(127.0)), res, res_scale, True,
+                  orc.KIND_I8, float(np.float32(127.0) / np.float32(out_dr)))
+    wts = ops.ConvWeights(pb["wq"], ops.I8, pb["scale"], pb["bias"])
+    st = ops.new_status()
+    out = ops.conv_forward(_dev(pb["xq"]), _dev(m_ref), ops.device_count(n), wts,
+                           act=ops.ACT_NONE, out_kind=ops.I8,
+                           inv_out_scale=float(np.float32(127.0) / np.float32(out_dr)),
+                           res=_dev(res), res_scale=res_scale, mid_kind=ops.I8,
+                           mid_inv_scale=float(np.float32(127.0) / np.float32(mid_dr)),
+                           mid_scale=float(np.float32(mid_dr) / np.float32(127.0)),
+                           res_relu=True, force_simt=simt, status=st)
+    torch.cuda.synchronize()
+    _status_ok(st)
+    assert np.array_equal(out.cpu().numpy(), ref)
+
+
+def test_strided_conv_int8_through_down_map():
+    ops = _ops()
+    grid, n = (41, 180, 180), 20000
+    pb = int8_problem(n, 16, 32, grid, seed=8)
+    roc, rdm, _, og, rn = orc.down_map(pb["coords"], grid, (3, 3, 3), (2, 2, 2), (1, 1, 1))
+    ref = orc.conv_i8(pb["xq"], rdm, rn, pb["wq"], pb["scale"], pb["bias"], orc.ACT_RELU,
+                      orc.KIND_I8, 20.0)
+    dc, n_ptr, st = _dev(pb["coords"]), ops.device_count(n), ops.new_status()
+    table = ops.hash_build(dc, n_ptr, grid, status=st)
+    oc, n_out, dm, _, _ = ops.down_map(dc, n_ptr, grid, table, (3, 3, 3), (2, 2, 2), (1, 1, 1),
+                                       status=st)
+    wts = ops.ConvWeights(pb["wq"], ops.I8, pb["scale"], pb["bias"])
+    out = ops.conv_forward(_dev(pb["xq"]), dm, n_out, wts, act=ops.ACT_RELU, out_kind=ops.I8,
+                           inv_out_scale=20.0, status=st)
+    torch.cuda.synchronize()
+    _status_ok(st)
+    assert int(n_out.item()) == rn
+    assert np.array_equal(out.cpu().numpy()[:rn], ref)
+
+
+# ---------------------------------------------------------------- elementwise
+@pytest.mark.parametrize("ak,bk,ok", [(1, 1, 1), (0, 0, 1), (0, 0, 0), (1, 0, 0)])
+@pytest.mark.parametrize("ch", [16, 24])
+def test_add_relu(ak, bk, ok, ch):
+    ops = _ops()
+    rng = np.random.default_rng(ak * 4 + bk * 2 + ok)
+    n = 3001
+
+    def mk(kind):
+        return (rng.integers(-128, 128, (n, ch)).astype(np.int8) if kind
+                else rng.standard_normal((n, ch)).astype(np.float16))
+    a, b = mk(ak), mk(bk)
+    ref = orc.add(a, 0.05, b, 0.021, True, ok, 9.3)
+    out = ops.add(_dev(a), 0.05, _dev(b), 0.021, ops.device_count(n), True, ok, 9.3)
+    assert np.array_equal(out.cpu().numpy().view(np.uint8), ref.view(np.uint8))
+
+
+def test_relu_and_convert():
+    ops = _ops()
+    rng = np.random.default_rng(0)
+    n = 1000
+    x8 = rng.integers(-128, 128, (n, 16)).astype(np.int8)
+    xh = rng.standard_normal((n, 16)).astype(np.float16)
+    n_ptr = ops.device_count(n)
+    assert np.array_equal(ops.relu(_dev(x8), n_ptr).cpu().numpy(), orc.relu(x8))
+    assert np.array_equal(ops.relu(_dev(xh), n_ptr).cpu().numpy().view(np.uint16),
+                          orc.relu(xh).view(np.uint16))
+    q = ops.convert(_dev(xh), ops.I8, 16, float(np.float32(127.0) / np.float32(3.0)), n_ptr)
+    assert np.array_equal(q.cpu().numpy(), orc.quantize_f16(xh, 3.0))
+
+
+@pytest.mark.parametrize("perm", [None, (0, 2, 1)])
+@pytest.mark.parametrize("kind", [0, 1])
+def test_scatter_dense(perm, kind):
+    ops = _ops()
+    grid, n, ch = (2, 180, 180), 7000, 128
+    coords = scenes.make_coords(n, grid, 2)
+    rng = np.random.default_rng(1)
+    feat = (rng.integers(-128, 128, (n, ch)).astype(np.int8) if kind
+            else rng.standard_normal((n, ch)).astype(np.float16))
+    ref = orc.scatter_dense(feat, coords, grid, 1, 0.02, perm)
+    out = ops.scatter_dense(_dev(feat), _dev(coords), ops.device_count(n), grid, 1, 0.02, perm)
+    assert np.array_equal(out.cpu().numpy().view(np.uint16), ref.view(np.uint16))
+
+
+# ------------------------------------------------------------------ voxelizer
+@pytest.mark.parametrize("kind", ["f32", "f16"])
+def test_voxelizer_matches_sequential_reference(kind, golden_dir):
+    ops = _ops()
+    if kind == "f32":
+        pts = scenes.make_points(120000, seed=3)
+    else:
+        pts = np.load(os.path.join(golden_dir, "sweep_points.npz"))["points"]
+    prange, vs = scenes.CENTERPOINT_RANGE, scenes.CENTERPOINT_VOXEL
+    gxyz = (1440, 1440, 40)
+    rf, rc, rn = orc.voxelize(pts, prange, vs, gxyz, 160000, 10, 0)
+    params = ops.voxel_params(prange, vs, gxyz, 5, 0 if kind == "f32" else 1, 10, 160000, 0)
+    st = ops.new_status()
+    feat, idx, n_ptr = ops.voxelize(_dev(pts), params, status=st)
+    torch.cuda.synchronize()
+    _status_ok(st)
+    n = int(n_ptr.item())
+    assert n == rn
+    assert np.array_equal(idx.cpu().numpy()[:n], rc)
+    assert np.array_equal(feat.cpu().numpy()[:n].view(np.uint16), rf.view(np.uint16))
+
+
+def test_voxelizer_max_voxels_clips():
+    ops = _ops()
+    from lidar_ai_solution_b200 import cabi
+    pts = scenes.make_points(20000, seed=9)
+    prange, vs, gxyz = scenes.CENTERPOINT_RANGE, scenes.CENTERPOINT_VOXEL, (1440, 1440, 40)
+    rf, rc, rn = orc.voxelize(pts, prange, vs, gxyz, 1000, 10, 1)
+    params = ops.voxel_params(prange, vs, gxyz, 5, 0, 10, 1000, 1)
+    st = ops.new_status()
+    feat, idx, n_ptr = ops.voxelize(_dev(pts), params, status=st)
+    torch.cuda.synchronize()
+    assert rn > 1000 and int(n_ptr.item()) == 1000
+    assert int(st.cpu().numpy()[0]) & cabi.ST_OVERFLOW
+    assert np.array_equal(idx.cpu().numpy(), rc)
+    assert np.array_equal(feat.cpu().numpy().view(np.uint16), rf.view(np.uint16))
