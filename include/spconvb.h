@@ -226,6 +226,188 @@ SPCONVB_API int spconvb_voxelize(const spconvb_voxel_params* p, const void* poin
                                  int32_t* indices, uint32_t* n_voxels_ptr, uint32_t* status,
                                  void* stream);
 
+/* ------------------------------------------------------------------ engine
+ * A whole backbone behind the C ABI.  These are the entry points the C++
+ * `spconv::` classes (include/spconv/engine.hpp) are written on; they mirror
+ * EngineBuilder / Engine of the reference one to one
+ * (libraries/3DSparseConvolution/libspconv/include/spconv/engine.hpp:55-167).
+ * Tensors are referred to by the integer ids the push functions return
+ * (negative = SPCONVB_E_*).  Precision: 1 = fp16, 2 = int8 (the reference's
+ * Precision enum); layout 1 = NCHW. */
+
+typedef struct spconvb_builder spconvb_builder;
+typedef struct spconvb_engine spconvb_engine;
+
+#define SPCONVB_PRECISION_FP16 1
+#define SPCONVB_PRECISION_INT8 2
+
+/* build flags */
+#define SPCONVB_BUILD_KEEP_TENSORS 1u   /* no buffer reuse: every tensor stays readable */
+#define SPCONVB_BUILD_NO_FUSION 2u      /* run Add / ReLU as their own kernels */
+#define SPCONVB_BUILD_FORCE_SIMT 4u     /* CUDA-core convolution everywhere */
+
+SPCONVB_API spconvb_builder* spconvb_builder_create(void);
+SPCONVB_API void spconvb_builder_destroy(spconvb_builder* b);
+
+/* EngineBuilder::push_input (engine.hpp:99) */
+SPCONVB_API int spconvb_builder_input(spconvb_builder* b, const char* name);
+
+/* EngineBuilder::push_sparse_conv (engine.hpp:135-156).  weight: fp16 bits
+ * [cout][k0][k1][k2][cin]; bias fp16 bits [cout] or NULL. */
+SPCONVB_API int spconvb_builder_sparse_conv(
+    spconvb_builder* b, const char* name, int x, const uint16_t* weight,
+    const int32_t weight_shape[5], const float* weight_dynamic_ranges, int32_t n_ranges,
+    const uint16_t* bias, int32_t n_bias, const char* activation, const int32_t kernel_size[3],
+    const int32_t stride[3], const int32_t padding[3], const int32_t dilation[3],
+    float input_dynamic_range, int32_t submanifold, uint32_t max_output_points,
+    uint32_t fixed_launch_points, const char* rulebook, int32_t precision,
+    int32_t output_precision, const char* output_name, int32_t inverse);
+
+/* EngineBuilder::push_add (engine.hpp:100-107) */
+SPCONVB_API int spconvb_builder_add(spconvb_builder* b, const char* name, int a, int bb,
+                                    float a_dynamic_range, float b_dynamic_range,
+                                    const char* output_name, int32_t precision,
+                                    int32_t output_precision, uint32_t fixed_launch_points);
+
+/* EngineBuilder::push_relu (engine.hpp:109-112) */
+SPCONVB_API int spconvb_builder_relu(spconvb_builder* b, const char* name, int x,
+                                     const char* output_name);
+
+/* EngineBuilder::push_dense (engine.hpp:114-123) */
+SPCONVB_API int spconvb_builder_dense(spconvb_builder* b, const char* name, int x,
+                                      const char* format, const char* output_name,
+                                      const int32_t* input_spatial_shape, int32_t n_spatial,
+                                      const int32_t* output_shape, int32_t n_output_shape,
+                                      int32_t output_layout, float input_dynamic_range,
+                                      uint32_t input_bound);
+
+/* EngineBuilder::push_reshape / push_transpose (engine.hpp:125-133) */
+SPCONVB_API int spconvb_builder_reshape(spconvb_builder* b, const char* name, int x,
+                                        const int64_t* shape, int32_t n, const char* output_name);
+SPCONVB_API int spconvb_builder_transpose(spconvb_builder* b, const char* name, int x,
+                                          const int64_t* dims, int32_t n, const char* output_name);
+
+/* EngineBuilder::push_output (engine.hpp:158) */
+SPCONVB_API int spconvb_builder_output(spconvb_builder* b, int x);
+
+/* EngineBuilder::build (engine.hpp:161).  Uploads packed weights on `stream`
+ * and synchronises it.  Returns NULL and sets *err on failure. */
+SPCONVB_API spconvb_engine* spconvb_builder_build(spconvb_builder* b, int32_t precision,
+                                                  uint32_t flags, void* stream, int* err);
+
+/* spconv::load_engine_from_onnx
+ * (libraries/3DSparseConvolution/src/onnx-parser.cpp:101-231; exported by the
+ * v1.0 library, CUDA-CenterPoint/3rdparty/libspconv/include/spconv/engine.hpp:103-104).
+ * Reads the ONNX protobuf wire format directly; no protobuf library needed. */
+SPCONVB_API spconvb_engine* spconvb_engine_load_onnx(const char* path, int32_t precision,
+                                                     uint32_t flags,
+                                                     uint32_t fixed_launch_points, void* stream,
+                                                     int* err);
+
+SPCONVB_API void spconvb_engine_destroy(spconvb_engine* e);
+
+/* Engine::forward of the v1.0 interface
+ * (CUDA-CenterPoint/3rdparty/libspconv/include/spconv/engine.hpp:73-77):
+ * features fp16 [n][C] and indices int32 [n][4] in device memory, used in
+ * place; n known on the host.  Asynchronous on `stream`; outputs are valid once
+ * the stream has run.  The first call for a given grid allocates buffers (and
+ * synchronises): make it before any stream capture. */
+SPCONVB_API int spconvb_engine_forward(spconvb_engine* e, const void* features, uint32_t n,
+                                       const int32_t* indices, const int32_t grid[3],
+                                       int32_t batch, void* stream);
+
+/* Engine::forward(stream) of the v1.3 interface with a DDS row count
+ * (engine.hpp:48-49,71): buffers hold up to `cap_rows` rows, the device word
+ * *n_dev says how many are valid.  Capturable in a CUDA graph once the grid
+ * has been seen by spconvb_engine_prepare or an earlier forward. */
+SPCONVB_API int spconvb_engine_forward_dds(spconvb_engine* e, const void* features,
+                                           const int32_t* indices, uint32_t cap_rows,
+                                           const uint32_t* n_dev, const int32_t grid[3],
+                                           int32_t batch, void* stream);
+
+/* Allocate everything for a grid ahead of time (synchronises). */
+SPCONVB_API int spconvb_engine_prepare(spconvb_engine* e, const int32_t grid[3], int32_t batch);
+
+SPCONVB_API int spconvb_engine_num_outputs(const spconvb_engine* e);
+
+/* Output i: device pointer, shape (up to 8 dims), element kind (SPCONVB_F16 /
+ * SPCONVB_I8), and whether it is dense.  For a sparse output shape = {cap, C}
+ * and spconvb_engine_tensor gives the rows. */
+SPCONVB_API int spconvb_engine_output(const spconvb_engine* e, int i, void** data,
+                                      int64_t shape[8], int32_t* ndim, int32_t* kind,
+                                      int32_t* dense);
+
+/* Any tensor by name (needs SPCONVB_BUILD_KEEP_TENSORS for intermediates):
+ * features pointer, element kind, channels as stored, int8 scale, coordinates
+ * pointer, device row-count pointer, capacity, grid. */
+typedef struct spconvb_tensor_view {
+  void* features;
+  int32_t kind;
+  int32_t channels;
+  float scale;
+  int32_t* coords;
+  uint32_t* n_ptr;
+  uint32_t cap;
+  int32_t grid[3];
+  int32_t dense;
+} spconvb_tensor_view;
+SPCONVB_API int spconvb_engine_tensor(const spconvb_engine* e, const char* name,
+                                      spconvb_tensor_view* view);
+
+/* Names of all tensors in execution order, '\n' separated (owned by the engine). */
+SPCONVB_API const char* spconvb_engine_tensor_names(const spconvb_engine* e);
+
+/* Per-step device times of one forward call, like the reference's verbose
+ * per-layer timing (spconv::EventTimer, libspconv/include/spconv/timer.hpp:22-51).
+ * Steps are the lines of spconvb_engine_describe.  Convolution, Add, ReLU,
+ * conversion and dense steps are run `reps` times, each behind a write of
+ * `flush_bytes` to `flush` (NULL: none) that evicts L2, and averaged; rulebook
+ * steps run once.  Synchronises after every step: a measurement aid, not a
+ * way to run inference. */
+SPCONVB_API int spconvb_engine_num_steps(const spconvb_engine* e);
+SPCONVB_API int spconvb_engine_profile(spconvb_engine* e, const void* features, uint32_t n,
+                                       const int32_t* indices, const int32_t grid[3],
+                                       int32_t batch, void* stream, float* step_ms,
+                                       int32_t max_steps, int32_t reps, void* flush,
+                                       size_t flush_bytes);
+
+/* Coordinate set i (the `cs=` column of spconvb_engine_describe): device row
+ * count, capacity and grid. */
+SPCONVB_API int spconvb_engine_coordset(const spconvb_engine* e, int i, uint32_t** n_ptr,
+                                        uint32_t* cap, int32_t grid[3]);
+
+/* Rulebook i of the engine (measurement helper): the map [kvol][cap], and the
+ * device row counts of its output and input coordinate sets. */
+SPCONVB_API int spconvb_engine_num_rules(const spconvb_engine* e);
+SPCONVB_API int spconvb_engine_rule(const spconvb_engine* e, int i, int32_t** map, uint32_t* cap,
+                                    int32_t* kvol, uint32_t** n_out_ptr, uint32_t** n_in_ptr);
+
+/* Copies device memory to the host after synchronising `stream` (test helper). */
+SPCONVB_API int spconvb_read_device(const void* device_src, void* host_dst, size_t bytes,
+                                    void* stream);
+
+/* cudaMemcpyAsync on `stream`; direction 0 = host to device, 1 = device to
+ * host, 2 = device to device.  For callers (ctypes, FFI) that hold raw pointers
+ * and no CUDA runtime binding of their own. */
+SPCONVB_API int spconvb_copy_async(void* dst, const void* src, size_t bytes, int32_t direction,
+                                   void* stream);
+
+/* Synchronises `stream` and copies the 4-word status block (SPCONVB_ST_*). */
+SPCONVB_API int spconvb_engine_status(const spconvb_engine* e, uint32_t out[4], void* stream);
+
+/* Kernels launched by the last forward call (host-side count of launches). */
+SPCONVB_API int spconvb_engine_last_launches(const spconvb_engine* e);
+
+/* Algorithmic work of the engine's graph for given per-coordinate-set counts is
+ * reported by spconvb_engine_describe: a '\n' separated text table, one line
+ * per executed step: "kind name rows_ptr_index cin cout kvol in_bytes out_bytes". */
+SPCONVB_API const char* spconvb_engine_describe(const spconvb_engine* e);
+
+/* Logging (spconv::set_logger_level, engine.hpp:171): 0 verbose, 1 warn, 2 error, 99 quiet. */
+SPCONVB_API void spconvb_set_log_level(int32_t level);
+typedef void (*spconvb_log_fn)(int32_t level, const char* message);
+SPCONVB_API void spconvb_set_log_callback(spconvb_log_fn fn);
+
 #ifdef __cplusplus
 }
 #endif

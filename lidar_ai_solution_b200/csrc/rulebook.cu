@@ -43,20 +43,21 @@ struct Kernel3 {
 };
 
 __global__ void subm_map_kernel(const int4* __restrict__ coords, const uint32_t* n_ptr,
-                                uint32_t cap, Grid3 g, Kernel3 kr,
+                                uint32_t cap, Grid3 g, Kernel3 kr, int kvol,
                                 const uint64_t* __restrict__ table, uint32_t mask,
                                 int32_t* __restrict__ map) {
   const uint32_t n = min(*n_ptr, cap);
-  const int k = blockIdx.y;
-  const int k2 = k % kr.k[2], k1 = (k / kr.k[2]) % kr.k[1], k0 = k / (kr.k[2] * kr.k[1]);
-  const int d0 = (k0 - kr.k[0] / 2) * kr.d[0];
-  const int d1 = (k1 - kr.k[1] / 2) * kr.d[1];
-  const int d2 = (k2 - kr.k[2] / 2) * kr.d[2];
-  const bool centre = (d0 | d1 | d2) == 0;
-  for (uint32_t row = blockIdx.x * blockDim.x + threadIdx.x; row < n;
-       row += gridDim.x * blockDim.x) {
+  const unsigned long long work = (unsigned long long)n * kvol;
+  for (unsigned long long idx = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
+       idx < work; idx += (unsigned long long)gridDim.x * blockDim.x) {
+    const int k = (int)(idx / n);
+    const uint32_t row = (uint32_t)(idx - (unsigned long long)k * n);
+    const int k2 = k % kr.k[2], k1 = (k / kr.k[2]) % kr.k[1], k0 = k / (kr.k[2] * kr.k[1]);
+    const int d0 = (k0 - kr.k[0] / 2) * kr.d[0];
+    const int d1 = (k1 - kr.k[1] / 2) * kr.d[1];
+    const int d2 = (k2 - kr.k[2] / 2) * kr.d[2];
     int32_t r = -1;
-    if (centre) {
+    if ((d0 | d1 | d2) == 0) {
       r = (int32_t)row;
     } else {
       int4 c = __ldg(coords + row);
@@ -88,13 +89,15 @@ __host__ __device__ inline uint32_t down_words(const int32_t og[3], int batch) {
 }
 
 __global__ void down_mark_kernel(const int4* __restrict__ coords, const uint32_t* n_ptr,
-                                 uint32_t cap, Grid3 gin, Grid3 gout, Kernel3 kr,
+                                 uint32_t cap, Grid3 gin, Grid3 gout, Kernel3 kr, int kvol,
                                  uint32_t* bitmap) {
   const uint32_t n = min(*n_ptr, cap);
-  const int k = blockIdx.y;
-  const int kk[3] = {k / (kr.k[2] * kr.k[1]), (k / kr.k[2]) % kr.k[1], k % kr.k[2]};
-  for (uint32_t row = blockIdx.x * blockDim.x + threadIdx.x; row < n;
-       row += gridDim.x * blockDim.x) {
+  const unsigned long long work = (unsigned long long)n * kvol;
+  for (unsigned long long idx = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
+       idx < work; idx += (unsigned long long)gridDim.x * blockDim.x) {
+    const int k = (int)(idx / n);
+    const uint32_t row = (uint32_t)(idx - (unsigned long long)k * n);
+    const int kk[3] = {k / (kr.k[2] * kr.k[1]), (k / kr.k[2]) % kr.k[1], k % kr.k[2]};
     int4 c = __ldg(coords + row);
     if ((unsigned)c.x >= (unsigned)gin.batch) continue;
     const int ci[3] = {c.y, c.z, c.w};
@@ -211,14 +214,16 @@ down_emit_kernel(DownWs ws, Grid3 gout, int4* __restrict__ out_coords, uint32_t*
 }
 
 __global__ void down_map_kernel(const int4* __restrict__ out_coords, const uint32_t* n_out_ptr,
-                                uint32_t cap_out, Grid3 gin, Kernel3 kr,
+                                uint32_t cap_out, Grid3 gin, Kernel3 kr, int kvol,
                                 const uint64_t* __restrict__ in_table, uint32_t in_mask,
                                 int32_t* __restrict__ map) {
   const uint32_t n = min(*n_out_ptr, cap_out);
-  const int k = blockIdx.y;
-  const int k2 = k % kr.k[2], k1 = (k / kr.k[2]) % kr.k[1], k0 = k / (kr.k[2] * kr.k[1]);
-  for (uint32_t row = blockIdx.x * blockDim.x + threadIdx.x; row < n;
-       row += gridDim.x * blockDim.x) {
+  const unsigned long long work = (unsigned long long)n * kvol;
+  for (unsigned long long idx = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
+       idx < work; idx += (unsigned long long)gridDim.x * blockDim.x) {
+    const int k = (int)(idx / n);
+    const uint32_t row = (uint32_t)(idx - (unsigned long long)k * n);
+    const int k2 = k % kr.k[2], k1 = (k / kr.k[2]) % kr.k[1], k0 = k / (kr.k[2] * kr.k[1]);
     int4 c = __ldg(out_coords + row);
     int p0 = c.y * kr.s[0] - kr.p[0] + k0 * kr.d[0];
     int p1 = c.z * kr.s[1] - kr.p[1] + k1 * kr.d[1];
@@ -229,6 +234,15 @@ __global__ void down_map_kernel(const int4* __restrict__ out_coords, const uint3
       r = hash_lookup(in_table, in_mask, voxel_key(c.x, p0, p1, p2, gin));
     map[(size_t)k * cap_out + row] = r;
   }
+}
+
+// Fixed-size grids: a multiple of the SM count, independent of the row count.
+static int flat_blocks(unsigned long long work_cap) {
+  unsigned long long b = (work_cap + kThreads - 1) / kThreads;
+  const unsigned long long most = (unsigned long long)kSmCount * 8;
+  if (b > most) b = most;
+  if (b < 1) b = 1;
+  return (int)b;
 }
 
 static bool grid_fits(const int32_t g[3], int batch) {
@@ -273,7 +287,7 @@ int spconvb_hash_build(const int32_t* coords, const uint32_t* n_ptr, uint32_t ca
   if (!(flags & SPCONVB_FLAG_PREZEROED))
     SPCONVB_CUDA_TRY(cudaMemsetAsync(table, 0, sizeof(uint64_t) * (size_t)slots, st));
   if (launch_rows == 0 || launch_rows > cap) launch_rows = cap;
-  hash_build_kernel<<<blocks_for(launch_rows, kThreads), kThreads, 0, st>>>(
+  hash_build_kernel<<<flat_blocks(launch_rows), kThreads, 0, st>>>(
       (const int4*)coords, n_ptr, cap, make_grid(grid, batch), table, slots - 1, status);
   SPCONVB_LAUNCH_CHECK();
   return SPCONVB_OK;
@@ -295,9 +309,10 @@ int spconvb_subm_map(const int32_t* coords, const uint32_t* n_ptr, uint32_t cap,
   const int kvol = ksize[0] * ksize[1] * ksize[2];
   if (kvol > 65535) return SPCONVB_E_ARG;
   if (launch_rows == 0 || launch_rows > cap) launch_rows = cap;
-  dim3 grid_dim(blocks_for(launch_rows, kThreads), kvol);
-  subm_map_kernel<<<grid_dim, kThreads, 0, (cudaStream_t)stream>>>(
-      (const int4*)coords, n_ptr, cap, make_grid(grid, batch), kr, table, slots - 1, map);
+  subm_map_kernel<<<flat_blocks((unsigned long long)launch_rows * kvol), kThreads, 0,
+                    (cudaStream_t)stream>>>((const int4*)coords, n_ptr, cap,
+                                            make_grid(grid, batch), kr, kvol, table, slots - 1,
+                                            map);
   SPCONVB_LAUNCH_CHECK();
   return SPCONVB_OK;
 }
@@ -349,19 +364,16 @@ int spconvb_down_map(const int32_t* in_coords, const uint32_t* n_in_ptr, uint32_
   }
   Grid3 gin = make_grid(in_grid, batch), gout = make_grid(og, batch);
   if (launch_rows == 0 || launch_rows > cap_in) launch_rows = cap_in;
-  dim3 mark_grid(blocks_for(launch_rows, kThreads), kvol);
-  down_mark_kernel<<<mark_grid, kThreads, 0, st>>>((const int4*)in_coords, n_in_ptr, cap_in, gin,
-                                                   gout, kr, ws.bitmap);
+  down_mark_kernel<<<flat_blocks((unsigned long long)launch_rows * kvol), kThreads, 0, st>>>(
+      (const int4*)in_coords, n_in_ptr, cap_in, gin, gout, kr, kvol, ws.bitmap);
   SPCONVB_LAUNCH_CHECK();
   down_scan_kernel<<<ws.blocks, kScanThreads, 0, st>>>(ws);
   SPCONVB_LAUNCH_CHECK();
   down_emit_kernel<<<ws.blocks, kScanThreads, 0, st>>>(ws, gout, (int4*)out_coords, n_out_ptr,
                                                        cap_out, out_table, out_slots - 1, status);
   SPCONVB_LAUNCH_CHECK();
-  uint32_t out_launch = cap_out;
-  dim3 map_grid(blocks_for(out_launch, kThreads), kvol);
-  down_map_kernel<<<map_grid, kThreads, 0, st>>>((const int4*)out_coords, n_out_ptr, cap_out,
-                                                 gin, kr, in_table, in_slots - 1, map);
+  down_map_kernel<<<flat_blocks((unsigned long long)cap_out * kvol), kThreads, 0, st>>>(
+      (const int4*)out_coords, n_out_ptr, cap_out, gin, kr, kvol, in_table, in_slots - 1, map);
   SPCONVB_LAUNCH_CHECK();
   return SPCONVB_OK;
 }

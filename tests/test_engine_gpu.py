@@ -1,0 +1,320 @@
+"""Whole-backbone parity through the engine C ABI (ONNX file -> load -> forward)
+against the CPU oracle's node-by-node execution of the same model.
+
+Tolerances: int8 tensors identical (0 LSB) wherever the arithmetic is exact, i.e.
+with the CUDA-core fp16 kernels, and per layer on the tensor-core path; fp16
+tensors within 1e-2 of the layer's absmax on the tensor-core path."""
+import os
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+
+from lidar_ai_solution_b200 import models, scenes  # noqa: E402
+from oracle import graph_oracle, oracle as orc  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+GRID = (41, 360, 360)
+
+
+def _frame(n, grid=GRID, seed=0):
+    coords = scenes.make_coords(n, grid, seed)
+    feats = scenes.make_point_features(coords, seed)
+    return feats, coords
+
+
+def _dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def _engine_mod():
+    from lidar_ai_solution_b200 import engine
+    return engine
+
+
+def _small_model(kind="centerpoint", seed=0):
+    return models.scn_backbone(kind, seed=seed, grid_zyx=GRID, output_bound=40000)
+
+
+def _quantized(kind, feats, coords, seed=0):
+    eng = _engine_mod()
+    model = _small_model(kind, seed)
+    ranges = eng.calibrate(model, _dev(feats), _dev(coords), GRID)
+    return models.quantize(model, ranges)
+
+
+def _compare_all(e, T, exact):
+    worst = 0.0
+    for tid, ref in T.items():
+        if tid == "0":
+            continue
+        got = e.tensor(tid)
+        n = len(ref["feat"])
+        assert got["n"] == n, "tensor %s: %d rows, oracle %d" % (tid, got["n"], n)
+        if got["coords"] is not None:
+            assert np.array_equal(got["coords"][:n].cpu().numpy(), ref["coords"])
+        g = got["features"][:n].cpu().numpy()
+        assert g.dtype == ref["feat"].dtype, "tensor %s stored as %s" % (tid, g.dtype)
+        if exact or g.dtype == np.int8:
+            if exact:
+                assert np.array_equal(g.view(np.uint8), ref["feat"].view(np.uint8)), tid
+        else:
+            r = ref["feat"].astype(np.float32)
+            err = float(np.abs(g.astype(np.float32) - r).max()) / max(float(np.abs(r).max()), 1e-6)
+            worst = max(worst, err)
+            assert err <= 1e-2, "tensor %s: relative error %g" % (tid, err)
+    return worst
+
+
+@pytest.mark.parametrize("kind", ["centerpoint", "bevfusion"])
+def test_fp16_backbone_per_layer(kind):
+    eng = _engine_mod()
+    feats, coords = _frame(12000)
+    model = _small_model(kind)
+    outs, T = graph_oracle.run(model, feats, coords, GRID, "fp16")
+    e = eng.Engine.from_model(model, eng.PRECISION_FP16, eng.BUILD_KEEP_TENSORS | eng.BUILD_NO_FUSION)
+    e.forward(_dev(feats), _dev(coords), GRID)
+    torch.cuda.synchronize()
+    assert e.status()[0] == 0
+    _compare_all(e, T, exact=False)
+    dense = e.output(0).cpu().numpy().astype(np.float32)
+    ref = outs[0].astype(np.float32)
+    assert dense.shape == ref.shape == tuple(model["outputs"][0][1])
+    assert float(np.abs(dense - ref).max()) <= 1e-2 * float(np.abs(ref).max())
+    assert float(np.mean((dense != 0) != (ref != 0))) < 1e-3
+
+
+@pytest.mark.parametrize("fusion", [False, True])
+def test_fp16_backbone_cuda_core_path_is_bit_exact(fusion):
+    eng = _engine_mod()
+    feats, coords = _frame(6000, seed=1)
+    model = _small_model("centerpoint", seed=1)
+    outs, T = graph_oracle.run(model, feats, coords, GRID, "fp16")
+    flags = eng.BUILD_FORCE_SIMT | (0 if fusion else eng.BUILD_KEEP_TENSORS | eng.BUILD_NO_FUSION)
+    e = eng.Engine.from_model(model, eng.PRECISION_FP16, flags)
+    e.forward(_dev(feats), _dev(coords), GRID)
+    torch.cuda.synchronize()
+    assert e.status()[0] == 0
+    if not fusion:
+        _compare_all(e, T, exact=True)
+    assert np.array_equal(e.output(0).cpu().numpy().view(np.uint16), outs[0].view(np.uint16))
+
+
+@pytest.mark.parametrize("kind", ["centerpoint", "bevfusion"])
+@pytest.mark.parametrize("fusion", [False, True])
+def test_int8_backbone_exact_with_cuda_core_fp16_layers(kind, fusion):
+    """With the fp16 layers on the CUDA-core kernel every operation of the int8 model is
+    defined exactly, so all tensors and the dense output must be identical to the oracle,
+    fused epilogues included."""
+    eng = _engine_mod()
+    feats, coords = _frame(9000, seed=2)
+    model = _quantized(kind, feats, coords, seed=2)
+    outs, T = graph_oracle.run(model, feats, coords, GRID, "int8")
+    flags = eng.BUILD_FORCE_SIMT | (0 if fusion else eng.BUILD_KEEP_TENSORS | eng.BUILD_NO_FUSION)
+    e = eng.Engine.from_model(model, eng.PRECISION_INT8, flags)
+    e.forward(_dev(feats), _dev(coords), GRID)
+    torch.cuda.synchronize()
+    assert e.status()[0] == 0
+    if not fusion:
+        _compare_all(e, T, exact=True)
+    assert np.array_equal(e.output(0).cpu().numpy().view(np.uint16), outs[0].view(np.uint16))
+
+
+def _replay_layers(model, e, precision, in_coords):
+    """Per-layer parity on the tensor-core path: every conv (+Add+Relu) is re-run on the
+    oracle from the engine's own input tensors; int8 results must be identical, fp16 within
+    1e-2 of the layer's absmax."""
+    kind, dr = graph_oracle.resolve(model, precision)
+    nodes = model["nodes"]
+    checked = 0
+    for n in nodes:
+        if n["op"] != "conv":
+            continue
+        src = e.tensor(n["x"])
+        x = src["features"][: src["n"]].cpu().numpy()
+        c = (src["coords"][: src["n"]].cpu().numpy() if src["coords"] is not None
+             else None)
+        if c is None:
+            c = in_coords  # the input's coordinates belong to the caller
+        # run the single node with the engine's stored representation of its input
+        T0 = dict(feat=x, coords=c, grid=src["grid"], kind="i8" if x.dtype == np.int8 else "f16",
+                  dr=src["scale"] * 127.0)
+        ref = _run_node(n, T0, kind, dr, precision)
+        got = e.tensor(n["out"])
+        g = got["features"][: got["n"]].cpu().numpy()
+        assert got["n"] == len(ref)
+        if g.dtype == np.int8 and x.dtype == np.int8:
+            assert int(np.abs(g.astype(np.int32) - ref.astype(np.int32)).max()) == 0, n["name"]
+        else:
+            r = ref.astype(np.float32)
+            scale = max(float(np.abs(r).max()), 1e-6)
+            lim = 1.0 if g.dtype == np.int8 else 1e-2 * scale
+            assert float(np.abs(g.astype(np.float32) - r).max()) <= lim, n["name"]
+        checked += 1
+    return checked
+
+
+def _run_node(n, src, kind, dr, precision):
+    F32 = np.float32
+    compute = graph_oracle._eff(precision, n.get("precision", "fp16"))
+    if n["subm"]:
+        m, _ = orc.subm_map(src["coords"], src["grid"], n["kernel_size"], n["dilation"])
+        n_out = len(src["coords"])
+    else:
+        oc, m, _, _, n_out = orc.down_map(src["coords"], src["grid"], n["kernel_size"],
+                                          n["stride"], n["padding"], n["dilation"],
+                                          cap=n["output_bound"])
+        n_out = len(oc)
+    w16 = np.ascontiguousarray(n["weight"], np.float16)
+    w16 = w16.reshape(w16.shape[0], -1, w16.shape[-1])
+    bias = n["bias"].astype(np.float32)
+    act = orc.ACT_RELU if n["activation"] == "ReLU" else orc.ACT_NONE
+    okind = orc.KIND_I8 if kind[n["out"]] == "i8" else orc.KIND_F16
+    inv_out = float(F32(127.0) / F32(dr[n["out"]])) if okind == orc.KIND_I8 else 1.0
+    if compute == "int8":
+        if src["kind"] == "i8":
+            xq, in_scale = src["feat"], F32(src["dr"]) / F32(127.0)
+        else:
+            xq = orc.quantize_f16(src["feat"], n["input_dynamic_range"])
+            in_scale = F32(n["input_dynamic_range"]) / F32(127.0)
+        amax = np.asarray(n["weight_dynamic_ranges"], np.float32)
+        wq = orc.quantize_weights(w16.astype(np.float32), amax)
+        scale = (in_scale * (amax / F32(127.0))).astype(np.float32)
+        return orc.conv_i8(xq, m, n_out, wq, scale, bias, act, okind, inv_out)
+    x = src["feat"]
+    if src["kind"] == "i8":
+        x = (x.astype(np.float32) * (F32(src["dr"]) / F32(127.0))).astype(np.float16)
+    return orc.conv_f16(x, m, n_out, w16, bias, act, okind, inv_out)
+
+
+def test_int8_backbone_tensor_core_per_layer():
+    eng = _engine_mod()
+    feats, coords = _frame(12000, seed=3)
+    model = _quantized("centerpoint", feats, coords, seed=3)
+    e = eng.Engine.from_model(model, eng.PRECISION_INT8, eng.BUILD_KEEP_TENSORS | eng.BUILD_NO_FUSION)
+    e.forward(_dev(feats), _dev(coords), GRID)
+    torch.cuda.synchronize()
+    assert e.status()[0] == 0
+    assert _replay_layers(model, e, "int8", coords) == 21
+    # the fused graph gives the same dense output as the unfused one
+    e2 = eng.Engine.from_model(model, eng.PRECISION_INT8, 0)
+    e2.forward(_dev(feats), _dev(coords), GRID)
+    torch.cuda.synchronize()
+    assert e2.status()[0] == 0
+    assert torch.equal(e.output(0), e2.output(0))
+    assert e2.last_launches() < e.last_launches()
+
+
+def test_dds_forward_and_cuda_graph_replay():
+    """Buffers sized for a bound, the valid row count read on the device; one captured graph
+    replayed with a shrinking row count (the reference's stress pattern,
+    libraries/3DSparseConvolution/libspconv/example/infer.cpp:344-367)."""
+    eng = _engine_mod()
+    cap = 16000
+    feats, coords = _frame(cap, seed=4)
+    model = _quantized("centerpoint", feats[:9000], coords[:9000], seed=4)
+    e = eng.Engine.from_model(model, eng.PRECISION_INT8, 0)
+    e.prepare(GRID)
+    df, dc = _dev(feats), _dev(coords)
+    n_dev = torch.zeros(1, dtype=torch.int32, device="cuda")
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        n_dev.fill_(cap)
+        e.forward_dds(df, dc, n_dev, GRID, stream=stream)  # warm-up outside capture
+        stream.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            e.forward_dds(df, dc, n_dev, GRID, stream=stream)
+    ref_engine = eng.Engine.from_model(model, eng.PRECISION_INT8, 0)
+    for n in (cap, 12345, 5000, 129, 1, 0):
+        n_dev.fill_(n)
+        g.replay()
+        torch.cuda.synchronize()
+        assert e.status()[0] == 0
+        got = e.output(0).clone()
+        ref_engine.forward(df[:max(n, 1)].contiguous(), dc[:max(n, 1)].contiguous(), GRID, n=n)
+        torch.cuda.synchronize()
+        assert torch.equal(got, ref_engine.output(0)), "n=%d" % n
+        if n == 0:
+            assert float(got.abs().max()) == 0.0
+
+
+def test_single_layer_sparse_output_and_bounds():
+    eng = _engine_mod()
+    feats, coords = _frame(5000, seed=5)
+    model = models.single_layer(5, 16, seed=5, output_bound=6000)
+    outs, T = graph_oracle.run(model, feats, coords, GRID, "fp16")
+    e = eng.Engine.from_model(model, eng.PRECISION_FP16, 0)
+    e.forward(_dev(feats), _dev(coords), GRID)
+    torch.cuda.synchronize()
+    got = e.output(0)[:5000].cpu().numpy().astype(np.float32)
+    ref = outs[0].astype(np.float32)
+    assert float(np.abs(got - ref).max()) <= 1e-2 * float(np.abs(ref).max())
+    big_f, big_c = _frame(7000, seed=6)
+    with pytest.raises(RuntimeError):
+        e.forward(_dev(big_f), _dev(big_c), GRID)  # more rows than output_bound
+
+
+def test_loader_rejects_bad_files(tmp_path):
+    eng = _engine_mod()
+    from lidar_ai_solution_b200 import onnx_writer
+    model = models.single_layer(5, 16)
+    blob = onnx_writer.serialize(model)
+    p = tmp_path / "trunc.onnx"
+    p.write_bytes(blob[: len(blob) // 2])
+    with pytest.raises(RuntimeError):
+        eng.Engine.from_onnx(str(p))
+    with pytest.raises(RuntimeError):
+        eng.Engine.from_onnx(str(tmp_path / "missing.onnx"))
+    p2 = tmp_path / "badop.onnx"
+    p2.write_bytes(blob.replace(b"SparseConvolution", b"SparseConvolutioX"))
+    with pytest.raises(RuntimeError):
+        eng.Engine.from_onnx(str(p2))
+
+
+def test_reference_frame_full_size_int8(golden_dir):
+    """The reference's 79 745-voxel CenterPoint frame at the full 41x1440x1440 grid through
+    the int8 backbone.  Per-stage row and pair counts equal the golden counts.  With the two
+    fp16 layers on the CUDA-core kernel the dense output equals the oracle's bit for bit; with
+    them on the tensor cores (fp32 sums in another order) a few int8 roundings flip and
+    propagate, so that run is held to the aggregate figures the reference itself reports for
+    engine-vs-PyTorch (libraries/3DSparseConvolution/README.md:73-81): cosine >= 0.9987."""
+    import json
+    eng = _engine_mod()
+    z = np.load(os.path.join(golden_dir, "fixture_coords.npz"))
+    counts = json.load(open(os.path.join(golden_dir, "fixture_counts.json")))["centerpoint"]
+    zyx = z["centerpoint_zyx"].astype(np.int32)
+    coords = np.concatenate([np.zeros((len(zyx), 1), np.int32), zyx], 1)
+    feats = scenes.make_point_features(coords, 0)
+    grid = (41, 1440, 1440)
+    model = models.scn_backbone("centerpoint", seed=0, grid_zyx=grid)
+    ranges = eng.calibrate(model, _dev(feats), _dev(coords), grid)
+    qm = models.quantize(model, ranges)
+    outs, _ = graph_oracle.run(qm, feats, coords, grid, "int8")
+    ref = outs[0].astype(np.float32)
+
+    e = eng.Engine.from_model(qm, eng.PRECISION_INT8, eng.BUILD_KEEP_TENSORS)
+    e.forward(_dev(feats), _dev(coords), grid)
+    torch.cuda.synchronize()
+    assert e.status()[0] == 0
+    rows = [r[1] for r in e.rules()]
+    want = sorted({c["n"] for c in counts} | {c["down_n"] for c in counts})
+    assert sorted(set(rows)) == want
+    pairs = sorted(int((m[:, :n_out] >= 0).sum().item()) for m, n_out, _ in e.rules())
+    assert pairs == sorted([c["subm_pairs"] for c in counts] + [c["down_pairs"] for c in counts])
+    got = e.output(0).cpu().numpy().astype(np.float32)
+    assert got.shape == (1, 256, 180, 180)
+    assert np.array_equal((got != 0).any(axis=1), (ref != 0).any(axis=1))  # same occupied cells
+    cos = float((got * ref).sum() / (np.linalg.norm(got) * np.linalg.norm(ref)))
+    mean_abs = float(np.abs(got - ref).mean())
+    assert cos >= 0.9987, (cos, mean_abs)
+    assert mean_abs <= 1e-3 * float(np.abs(ref).max()), (cos, mean_abs)
+    e.close()
+
+    exact = eng.Engine.from_model(qm, eng.PRECISION_INT8, eng.BUILD_FORCE_SIMT)
+    exact.forward(_dev(feats), _dev(coords), grid)
+    torch.cuda.synchronize()
+    assert exact.status()[0] == 0
+    assert np.array_equal(exact.output(0).cpu().numpy().view(np.uint16), outs[0].view(np.uint16))
