@@ -50,6 +50,7 @@ extern "C" {
 #define SPCONVB_E_UNSUPPORTED (-5)
 #define SPCONVB_E_STATE (-6)      /* call made in the wrong state */
 #define SPCONVB_E_DEVICE (-7)     /* status block reported a device-side error */
+#define SPCONVB_E_SCRATCH_LIMIT (-8) /* problem needs more than the built-in scratch area */
 
 /* device status bits (status[0]); status[1] = first offending row / count */
 #define SPCONVB_ST_HASH_FULL 1u
@@ -116,6 +117,39 @@ SPCONVB_API int spconvb_down_map(const int32_t* in_coords, const uint32_t* n_in_
                                  int32_t* out_coords, uint32_t* n_out_ptr, uint32_t cap_out,
                                  int32_t* map, uint64_t* out_table, uint32_t out_slots,
                                  uint32_t flags, uint32_t* status, void* stream);
+
+/* Allocation-free variant of spconvb_down_map.  It has no counterpart in the
+ * reference library; it exists for callers that are not allowed to allocate
+ * device memory at all: a perception stack that freezes its memory map after
+ * start-up (the usual rule on the automotive targets this code serves), or a
+ * host that runs the rulebook step from a callback in which cudaMalloc is
+ * forbidden or would stall every stream of the device.  Such a caller cannot
+ * provide the `workspace` of spconvb_down_map, so this entry point brings its
+ * own: SPCONVB_STATIC_SCRATCH_BYTES of device memory that are part of the
+ * library image (each GPU that loads the library holds them until exit).
+ *
+ * Arguments and results are those of spconvb_down_map without `workspace`;
+ * inputs, outputs and the optional output hash table are still the caller's.
+ *  - The output grid must fit: spconvb_down_workspace_bytes(out_grid, batch)
+ *    <= SPCONVB_STATIC_SCRATCH_BYTES (about 16 million output cells), else
+ *    SPCONVB_E_SCRATCH_LIMIT is returned and nothing is launched.
+ *  - Nothing is allocated or freed, here or in anything this calls.
+ *  - The first call on a device looks the scratch address up (once per device,
+ *    with that device current).  Make that first call outside stream capture.
+ *  - All calls on a device share the one scratch area.  It is cleared at the
+ *    start of every call, so back-to-back calls on one stream are fine; calls
+ *    that can overlap on the GPU (different streams, no dependency) race. */
+#define SPCONVB_STATIC_SCRATCH_BYTES (4u << 20)
+SPCONVB_API int spconvb_down_map_static(const int32_t* in_coords, const uint32_t* n_in_ptr,
+                                        uint32_t cap_in, uint32_t launch_rows,
+                                        const int32_t in_grid[3], int32_t batch,
+                                        const int32_t ksize[3], const int32_t stride[3],
+                                        const int32_t pad[3], const int32_t dilation[3],
+                                        const uint64_t* in_table, uint32_t in_slots,
+                                        int32_t* out_coords, uint32_t* n_out_ptr,
+                                        uint32_t cap_out, int32_t* map, uint64_t* out_table,
+                                        uint32_t out_slots, uint32_t flags, uint32_t* status,
+                                        void* stream);
 
 /* ------------------------------------------------------------- convolution
  * Replaces the closed gather-GEMM-scatter kernel behind

@@ -17,6 +17,8 @@ F16, I8 = 0, 1
 ACT_NONE, ACT_RELU = 0, 1
 ST_HASH_FULL, ST_DUPLICATE, ST_OVERFLOW, ST_TIMEOUT, ST_COORD_RANGE = 1, 2, 4, 8, 16
 FLAG_PREZEROED = 1
+E_SCRATCH_LIMIT = -8
+STATIC_SCRATCH_BYTES = 4 << 20
 
 
 class ConvParams(C.Structure):
@@ -53,6 +55,9 @@ SYMBOLS = {
     "spconvb_down_map": (C.c_int, [_VP, _VP, C.c_uint32, C.c_uint32, _I3, C.c_int32, _I3, _I3, _I3,
                                    _I3, _VP, C.c_uint32, _VP, _VP, _VP, C.c_uint32, _VP, _VP,
                                    C.c_uint32, C.c_uint32, _VP, _VP]),
+    "spconvb_down_map_static": (C.c_int, [_VP, _VP, C.c_uint32, C.c_uint32, _I3, C.c_int32, _I3, _I3,
+                                          _I3, _I3, _VP, C.c_uint32, _VP, _VP, C.c_uint32, _VP,
+                                          _VP, C.c_uint32, C.c_uint32, _VP, _VP]),
     "spconvb_conv_packed_bytes": (C.c_size_t, [C.c_int32] * 4),
     "spconvb_conv_pack_weights": (C.c_int, [C.c_int32] * 4 + [_VP, _VP]),
     "spconvb_conv_supported": (C.c_int, [C.c_int32] * 3),

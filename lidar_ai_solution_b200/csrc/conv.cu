@@ -64,6 +64,7 @@ const char* spconvb_error_string(int code) {
     case SPCONVB_E_UNSUPPORTED: return "unsupported operator or shape";
     case SPCONVB_E_STATE: return "call made in the wrong state";
     case SPCONVB_E_DEVICE: return "device-side status reported an error";
+    case SPCONVB_E_SCRATCH_LIMIT: return "output grid needs more than the built-in scratch area";
   }
   if (code > 0) return cudaGetErrorString((cudaError_t)code);
   return "unknown error";

@@ -6,6 +6,8 @@
 // Strided outputs are made unique and ordered without sorting: each candidate
 // output cell sets one bit in a bitmap over the output grid, an exclusive scan
 // of the per-word popcounts ranks the set bits, and the rank is the output row.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace spconvb {
@@ -258,6 +260,35 @@ static Grid3 make_grid(const int32_t g[3], int batch) {
   return r;
 }
 
+// ------------------------------------------------- allocation-free variant
+// Scratch for spconvb_down_map_static: part of the library image, so every GPU
+// that loads the library holds these bytes until the process exits.
+constexpr size_t kStaticScratchBytes = SPCONVB_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_down_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+static void* g_down_scratch_ptr[kMaxDevices] = {};
+static std::mutex g_down_scratch_mutex;
+
+// The array's name is only a host-side handle; the address kernels can use
+// comes from cudaGetSymbolAddress, asked once per device with that device current.
+static int static_scratch_for_current_device(void** out) {
+  int dev = -1;
+  cudaError_t ce = cudaGetDevice(&dev);
+  if (ce != cudaSuccess) return (int)ce;
+  if (dev < 0 || dev >= kMaxDevices) return SPCONVB_E_ARG;
+  std::lock_guard<std::mutex> lock(g_down_scratch_mutex);
+  if (!g_down_scratch_ptr[dev]) {
+    void* p = nullptr;
+    ce = cudaGetSymbolAddress(&p, g_down_scratch);
+    if (ce != cudaSuccess) return (int)ce;
+    if (!p) return SPCONVB_E_STATE;
+    g_down_scratch_ptr[dev] = p;
+  }
+  *out = g_down_scratch_ptr[dev];
+  return SPCONVB_OK;
+}
+
 }  // namespace spconvb
 
 using namespace spconvb;
@@ -377,5 +408,40 @@ int spconvb_down_map(const int32_t* in_coords, const uint32_t* n_in_ptr, uint32_
   SPCONVB_LAUNCH_CHECK();
   return SPCONVB_OK;
 }
+
+int spconvb_down_map_static(const int32_t* in_coords, const uint32_t* n_in_ptr, uint32_t cap_in,
+                            uint32_t launch_rows, const int32_t in_grid[3], int32_t batch,
+                            const int32_t ksize[3], const int32_t stride[3],
+                            const int32_t pad[3], const int32_t dilation[3],
+                            const uint64_t* in_table, uint32_t in_slots, int32_t* out_coords,
+                            uint32_t* n_out_ptr, uint32_t cap_out, int32_t* map,
+                            uint64_t* out_table, uint32_t out_slots, uint32_t flags,
+                            uint32_t* status, void* stream) {
+  if (!in_grid || !ksize || !stride || !pad || !dilation) return SPCONVB_E_ARG;
+  int32_t og[3];
+  for (int a = 0; a < 3; ++a) {
+    if (ksize[a] < 1 || stride[a] < 1 || dilation[a] < 1 || pad[a] < 0) return SPCONVB_E_ARG;
+    og[a] = spconvb_out_extent(in_grid[a], ksize[a], stride[a], pad[a], dilation[a]);
+    if (og[a] < 1) return SPCONVB_E_ARG;
+  }
+  const size_t need = spconvb_down_workspace_bytes(og, batch);
+  if (need == 0) return SPCONVB_E_RANGE;
+  if (need > kStaticScratchBytes) return SPCONVB_E_SCRATCH_LIMIT;
+  void* scratch = nullptr;
+  int rc = static_scratch_for_current_device(&scratch);
+  if (rc != SPCONVB_OK) return rc;
+  // The array still holds the previous call's bitmap: it is cleared on every
+  // call, whatever the caller says about its own buffers.
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t bitmap_bytes = sizeof(uint32_t) * (size_t)down_words(og, batch);
+  SPCONVB_CUDA_TRY(cudaMemsetAsync(scratch, 0, bitmap_bytes, st));
+  if (out_table && !(flags & SPCONVB_FLAG_PREZEROED))
+    SPCONVB_CUDA_TRY(cudaMemsetAsync(out_table, 0, sizeof(uint64_t) * (size_t)out_slots, st));
+  return spconvb_down_map(in_coords, n_in_ptr, cap_in, launch_rows, in_grid, batch, ksize, stride,
+                          pad, dilation, in_table, in_slots, scratch, out_coords, n_out_ptr,
+                          cap_out, map, out_table, out_slots, flags | SPCONVB_FLAG_PREZEROED,
+                          status, stream);
+}
+
 
 }  // extern "C"
