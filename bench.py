@@ -202,7 +202,7 @@ def run_reference(args, rank, world):
 # ------------------------------------------------------------------ GPU arm
 def run_gpu(args, rank, world, local_rank):
     import torch
-    from lidar_ai_solution_b200 import cabi, engine, onnx_writer
+    from lidar_ai_solution_b200 import cabi, engine, onnx_writer, sharding
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
@@ -219,7 +219,7 @@ def run_gpu(args, rank, world, local_rank):
     onnx_writer.save(qm, onnx_path)
 
     F, R = args.frames, max(1, min(args.replicas, args.frames))
-    frames = make_frames(F, 1000 * (rank + 1))
+    frames = [make_frames(1, s)[0] for s in sharding.frame_seeds(rank, F)]
     streams = [torch.cuda.Stream(device=dev) for _ in range(R)]
     engines = [engine.Engine.from_onnx(onnx_path, engine.PRECISION_INT8, 0, 0, dev)
                for _ in range(R)]
@@ -278,7 +278,6 @@ def run_gpu(args, rank, world, local_rank):
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
-        t_wall = time.perf_counter()
         start = torch.cuda.Event(enable_timing=True)
         end = torch.cuda.Event(enable_timing=True)
         with torch.cuda.stream(main):
@@ -294,18 +293,14 @@ def run_gpu(args, rank, world, local_rank):
         with torch.cuda.stream(main):
             end.record(main)
         torch.cuda.synchronize()
-        wall = time.perf_counter() - t_wall
-        ms = start.elapsed_time(end)
+        ms, frames_done = sharding.aggregate(start.elapsed_time(end), F * steps, dist, dev)
         if dist is not None:
-            t = torch.tensor([ms], dtype=torch.float64, device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
             dist.barrier()
-        return ms, wall
+        return ms, frames_done
 
     sampler = ClockSampler(local_rank)
     sampler.start()
-    ms_dev, _ = timed(args.steps, args.warmup, e2e=False)
+    ms_dev, total_frames = timed(args.steps, args.warmup, e2e=False)
     clocks = sampler.stop()
     ms_e2e, _ = timed(args.steps, args.warmup, e2e=True)
     for e in engines:
@@ -313,7 +308,6 @@ def run_gpu(args, rank, world, local_rank):
         if st[0]:
             raise RuntimeError("device status %s after the timed region" % st)
 
-    total_frames = F * world * args.steps
     voxels_per_frame = float(np.mean([len(f) for f, _ in frames]))
     value = total_frames / (ms_dev / 1000.0)
     e2e_value = total_frames / (ms_e2e / 1000.0)

@@ -338,6 +338,11 @@ SPCONVB_API spconvb_engine* spconvb_engine_load_onnx(const char* path, int32_t p
                                                      uint32_t fixed_launch_points, void* stream,
                                                      int* err);
 
+/* Parses a model file and writes a text summary into `buf` (one line per
+ * node: op, name, inputs, output, the attributes the loader uses).  Needs no
+ * GPU.  Returns SPCONVB_OK or the loader's error code. */
+SPCONVB_API int spconvb_onnx_inspect(const char* path, char* buf, size_t buf_bytes);
+
 SPCONVB_API void spconvb_engine_destroy(spconvb_engine* e);
 
 /* Engine::forward of the v1.0 interface

@@ -1,5 +1,8 @@
 // extern "C" surface of the builder and the engine (see include/spconvb.h).
+#include <stdio.h>
 #include <string.h>
+
+#include <string>
 
 #include "engine.hpp"
 
@@ -184,6 +187,50 @@ spconvb_engine* spconvb_engine_load_onnx(const char* path, int32_t precision, ui
   }
   if (err) *err = rc;
   return e;
+}
+
+int spconvb_onnx_inspect(const char* path, char* buf, size_t buf_bytes) {
+  if (!path || !buf || buf_bytes < 2) return SPCONVB_E_ARG;
+  Builder b;
+  buf[0] = 0;
+  const int rc = load_onnx(path, 0, &b);
+  if (rc != SPCONVB_OK) return rc;
+  std::string out;
+  char line[1024];
+  static const char* ops[] = {"Input", "SparseConvolution", "Add", "Relu", "ScatterDense",
+                              "Reshape", "Transpose"};
+  for (const GNode& n : b.nodes) {
+    const char* in0 = n.in0 >= 0 ? b.tensors[n.in0].name.c_str() : "-";
+    const char* in1 = n.in1 >= 0 ? b.tensors[n.in1].name.c_str() : "-";
+    snprintf(line, sizeof(line), "%s %s in=%s,%s out=%s", ops[n.op], n.name.c_str(), in0, in1,
+             b.tensors[n.out].name.c_str());
+    out += line;
+    if (n.op == OP_CONV) {
+      snprintf(line, sizeof(line),
+               " cin=%d cout=%d k=%d,%d,%d s=%d,%d,%d p=%d,%d,%d d=%d,%d,%d subm=%d relu=%d "
+               "bound=%u rulebook=%s prec=%d out_prec=%d in_dr=%.9g n_wdr=%zu bias=%zu",
+               n.cin, n.cout, n.ksize[0], n.ksize[1], n.ksize[2], n.stride[0], n.stride[1],
+               n.stride[2], n.pad[0], n.pad[1], n.pad[2], n.dil[0], n.dil[1], n.dil[2],
+               (int)n.subm, (int)n.relu_act, n.out_bound, n.rulebook.c_str(), n.prec, n.out_prec,
+               (double)n.in_dr, n.wdr.size(), n.bias.size());
+      out += line;
+    } else if (n.op == OP_ADD) {
+      snprintf(line, sizeof(line), " a_dr=%.9g b_dr=%.9g prec=%d out_prec=%d", (double)n.a_dr,
+               (double)n.b_dr, n.prec, n.out_prec);
+      out += line;
+    } else if (n.op == OP_DENSE) {
+      out += " format=" + n.format + " out_shape=";
+      for (int v : n.out_shape) out += std::to_string(v) + ",";
+    } else if (n.op == OP_RESHAPE || n.op == OP_TRANSPOSE) {
+      out += " dims=";
+      for (auto v : n.dims) out += std::to_string(v) + ",";
+    }
+    out += "\n";
+  }
+  for (int t : b.outputs) out += "Output " + b.tensors[t].name + "\n";
+  if (out.size() + 1 > buf_bytes) return SPCONVB_E_NOMEM;
+  memcpy(buf, out.c_str(), out.size() + 1);
+  return SPCONVB_OK;
 }
 
 void spconvb_engine_destroy(spconvb_engine* e) { delete e; }

@@ -41,6 +41,7 @@ SYMBOLS = {
     "spconvb_builder_build": (_VP, [_VP, C.c_int32, C.c_uint32, _VP, C.POINTER(C.c_int)]),
     "spconvb_engine_load_onnx": (_VP, [_CP, C.c_int32, C.c_uint32, C.c_uint32, _VP,
                                        C.POINTER(C.c_int)]),
+    "spconvb_onnx_inspect": (C.c_int, [_CP, _CP, C.c_size_t]),
     "spconvb_engine_destroy": (None, [_VP]),
     "spconvb_engine_forward": (C.c_int, [_VP, _VP, C.c_uint32, _VP, _I32P, C.c_int32, _VP]),
     "spconvb_engine_forward_dds": (C.c_int, [_VP, _VP, _VP, C.c_uint32, _VP, _I32P, C.c_int32,

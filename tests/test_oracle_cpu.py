@@ -1,0 +1,161 @@
+"""CPU-only checks that pin the oracle: golden counts of the reference's input
+fixtures, dense cross-correlation, the tensor container, quantisation rules."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from lidar_ai_solution_b200 import scenes
+from oracle import graph_oracle, oracle as orc
+
+STAGES = [((3, 3, 3), (2, 2, 2), (1, 1, 1)), ((3, 3, 3), (2, 2, 2), (1, 1, 1)),
+          ((3, 3, 3), (2, 2, 2), (0, 1, 1)), ((3, 1, 1), (2, 1, 1), (0, 0, 0))]
+
+
+def _fixture(golden_dir, key):
+    zyx = np.load(os.path.join(golden_dir, "fixture_coords.npz"))[key].astype(np.int32)
+    return np.concatenate([np.zeros((len(zyx), 1), np.int32), zyx], 1)
+
+
+@pytest.mark.parametrize("name,key", [("bevfusion", "bevfusion_zyx"),
+                                      ("centerpoint", "centerpoint_zyx")])
+def test_rulebook_counts_of_reference_frames(golden_dir, name, key):
+    """Per-stage voxel and pair counts of the reference's own sample frames."""
+    coords = _fixture(golden_dir, key)
+    gold = json.load(open(os.path.join(golden_dir, "fixture_counts.json")))[name]
+    assert orc.count_duplicates(coords, [41, 1440, 1440]) == 0
+    grid = [41, 1440, 1440]
+    for (k, s, p), g in zip(STAGES, gold):
+        _, pairs = orc.subm_map(coords, grid)
+        oc, _, dpairs, og, n_out = orc.down_map(coords, grid, k, s, p)
+        assert (len(coords), pairs, n_out, dpairs, og) == (
+            g["n"], g["subm_pairs"], g["down_n"], g["down_pairs"], g["down_grid"])
+        coords, grid = oc, og
+    assert grid == [2, 180, 180]   # 128 channels x 2 = the 256-channel BEV map
+
+
+def test_survey_figures_for_the_centerpoint_frame(golden_dir):
+    """The published frame: 79 745 voxels, 591 581 SubM pairs, 69 276 voxels after the first
+    stride-2 conv (figures computed independently when the reference was surveyed)."""
+    gold = json.load(open(os.path.join(golden_dir, "fixture_counts.json")))["centerpoint"]
+    assert [g["n"] for g in gold] == [79745, 69276, 29723, 10335]
+    assert [g["subm_pairs"] for g in gold] == [591581, 969672, 483025, 172003]
+    assert [g["down_n"] for g in gold] == [69276, 29723, 10335, 7658]
+    assert [g["down_pairs"] for g in gold] == [265739, 233074, 98648, 13673]
+
+
+def _dense_conv(x_sparse, coords, grid, w, stride, pad):
+    torch = pytest.importorskip("torch")
+    cin = x_sparse.shape[1]
+    dense = torch.zeros((1, cin, *grid), dtype=torch.float64)
+    dense[0, :, coords[:, 1], coords[:, 2], coords[:, 3]] = torch.from_numpy(
+        x_sparse.astype(np.float64)).T
+    wt = torch.from_numpy(w.astype(np.float64)).permute(0, 4, 1, 2, 3)  # [O,k0,k1,k2,I] -> OIDHW
+    return torch.nn.functional.conv3d(dense, wt, stride=stride, padding=pad)[0].numpy()
+
+
+@pytest.mark.parametrize("ksize,stride,pad,subm", [
+    ((3, 3, 3), (1, 1, 1), (1, 1, 1), True), ((3, 3, 3), (2, 2, 2), (1, 1, 1), False),
+    ((3, 3, 3), (2, 2, 2), (0, 1, 1), False), ((3, 1, 1), (2, 1, 1), (0, 0, 0), False)])
+def test_conv_equals_dense_cross_correlation_on_active_sites(ksize, stride, pad, subm):
+    rng = np.random.default_rng(0)
+    grid = (8, 16, 16)
+    coords = scenes.make_coords(300, grid, 1)
+    x = rng.standard_normal((300, 4)).astype(np.float32)
+    w = rng.standard_normal((6, *ksize, 4)).astype(np.float32)
+    dense = _dense_conv(x, coords, grid, w, stride, pad)
+    if subm:
+        m, _ = orc.subm_map(coords, grid, ksize)
+        oc, n_out = coords, len(coords)
+    else:
+        oc, m, _, og, n_out = orc.down_map(coords, grid, ksize, stride, pad)
+        assert list(dense.shape[1:]) == og
+        # every site the dense conv can reach from an active input is an output, and only those
+        reach = np.zeros(dense.shape[1:], bool)
+        ones = _dense_conv(np.ones((300, 1), np.float32), coords, grid,
+                           np.ones((1, *ksize, 1), np.float32), stride, pad)[0]
+        reach[ones > 0] = True
+        got = np.zeros_like(reach)
+        got[oc[:, 1], oc[:, 2], oc[:, 3]] = True
+        assert np.array_equal(got, reach)
+        keys = (oc[:, 1] * og[1] + oc[:, 2]) * og[2] + oc[:, 3]
+        assert np.all(np.diff(keys) > 0)           # canonical ascending order, no duplicates
+    y = orc.conv_f32(x, m, n_out, w.reshape(6, -1, 4))
+    ref = dense[:, oc[:, 1], oc[:, 2], oc[:, 3]].T
+    assert np.allclose(y, ref, rtol=1e-4, atol=1e-4)
+
+
+def test_int8_epilogue_rules():
+    """q = clamp(rint(x*127/dr)) with ties to even; weights clamp to +-127; y = fma(acc, s, b)."""
+    x = np.array([[0.5, 1.5, 2.5, -0.5, -1.5, 200.0, -200.0, 0.49]], np.float16)
+    q = orc.quantize_f16(x, 127.0)
+    assert q.tolist() == [[0, 2, 2, 0, -2, 127, -128, 0]]
+    w = np.array([[1.0, -1.0, 0.5, 3.0]], np.float32)
+    assert orc.quantize_weights(w, np.array([1.0], np.float32)).tolist() == [[127, -127, 64, 127]]
+    m = np.zeros((1, 1), np.int32)
+    xq = np.array([[10, -3]], np.int8)
+    wq = np.array([[[7, 5]]], np.int8)
+    y = orc.conv_i8(xq, m, 1, wq, np.array([0.25], np.float32), np.array([1.0], np.float32),
+                    orc.ACT_NONE, orc.KIND_F32)
+    assert y[0, 0] == np.float32(55 * 0.25 + 1.0)
+    yq = orc.conv_i8(xq, m, 1, wq, np.array([0.25], np.float32), np.array([1.0], np.float32),
+                     orc.ACT_RELU, orc.KIND_I8, 2.0)
+    assert yq[0, 0] == 30    # rint(14.75*2) = 30 (29.5 ties to even)
+
+
+def test_tensor_container_sample(golden_dir):
+    """The reference's tensor file format (tool/tensor.py:24-69): int32 magic 0x33ff1101,
+    ndim, dtype code, int32 dims, raw data."""
+    raw = open(os.path.join(golden_dir, "sample.tensor"), "rb").read()
+    magic, ndim, code, d0, d1 = np.frombuffer(raw[:20], np.int32)
+    assert (magic, ndim, code, d0, d1) == (0x33FF1101, 2, 2, 40, 5)
+    data = np.frombuffer(raw[20:], np.float16).reshape(d0, d1)
+    head = np.load(os.path.join(golden_dir, "fixture_coords.npz"))["centerpoint_feat_head"]
+    assert np.array_equal(data.view(np.uint16), head.view(np.uint16))
+    assert np.all(np.abs(data[:, :2].astype(np.float32)) <= 54.0)   # x, y inside the range
+
+
+def test_voxelizer_oracle_on_reference_sweep(golden_dir):
+    pts = np.load(os.path.join(golden_dir, "sweep_points.npz"))["points"]
+    feat, coords, total = orc.voxelize(pts, scenes.CENTERPOINT_RANGE, scenes.CENTERPOINT_VOXEL,
+                                       (1440, 1440, 40), 160000, 10, 0)
+    assert total == len(coords) and 0 < total < len(pts)
+    assert orc.count_duplicates(coords, [41, 1440, 1440]) == 0
+    # every voxel's mean lies inside the voxel it was assigned to
+    f = feat.astype(np.float32)
+    vx = np.floor((f[:, 0] + 54.0) / 0.075)
+    assert np.mean(np.abs(vx - coords[:, 3]) <= 1) > 0.999
+    # first voxel = first in-range point
+    r = scenes.CENTERPOINT_RANGE
+    p32 = pts.astype(np.float32)
+    inside = ((p32[:, 0] >= r[0]) & (p32[:, 0] < r[3]) & (p32[:, 1] >= r[1]) & (p32[:, 1] < r[4])
+              & (p32[:, 2] >= r[2]) & (p32[:, 2] < r[5]))
+    first = p32[np.argmax(inside)]
+    assert coords[0].tolist() == [0, int(np.floor((first[2] + 5.0) / 0.2)),
+                                  int(np.floor((first[1] + 54.0) / 0.075)),
+                                  int(np.floor((first[0] + 54.0) / 0.075))]
+
+
+def test_graph_oracle_int8_matches_float_model_closely():
+    """The int8 model tracks the fp16 model (quantisation noise only): a sanity check that
+    the scale plumbing (consumer-driven ranges) is coherent."""
+    from lidar_ai_solution_b200 import models
+    grid = (41, 180, 180)
+    coords = scenes.make_coords(3000, grid, 0)
+    feats = scenes.make_point_features(coords, 0)
+    model = models.scn_backbone("centerpoint", 0, grid_zyx=grid, output_bound=20000)
+    outs, T = graph_oracle.run(model, feats, coords, grid, "fp16")
+    ranges = {k: float(np.abs(v["feat"].astype(np.float32)).max()) for k, v in T.items()}
+    qm = models.quantize(model, ranges)
+    kind, dr = graph_oracle.resolve(qm, "int8")
+    assert kind["1"] == "f16" and kind[qm["nodes"][-3]["out"]] == "f16"   # conv_input, extra_conv
+    assert sum(v == "i8" for v in kind.values()) >= 25
+    q_outs, _ = graph_oracle.run(qm, feats, coords, grid, "int8")
+    a, b = outs[0].astype(np.float32).ravel(), q_outs[0].astype(np.float32).ravel()
+    assert outs[0].shape == (1, 256, 23, 23)
+    cos = float(a @ b / (np.linalg.norm(a) * np.linalg.norm(b)))
+    assert cos > 0.98, cos
+    # a loader precision of fp16 ignores the int8 attributes
+    f_outs, _ = graph_oracle.run(qm, feats, coords, grid, "fp16")
+    assert np.array_equal(f_outs[0].view(np.uint16), outs[0].view(np.uint16))
