@@ -188,7 +188,7 @@ SPCONVB_API size_t spconvb_conv_packed_bytes(int32_t compute, int32_t cin, int32
 SPCONVB_API int spconvb_conv_pack_weights(int32_t compute, int32_t cin, int32_t cout,
                                           int32_t kvol, const void* w, void* dst);
 
-/* 1 when the tensor-core kernel covers this shape. */
+/* 1 when the tensor-core kernel covers this shape (and kvol <= 27). */
 SPCONVB_API int spconvb_conv_supported(int32_t compute, int32_t cin, int32_t cout);
 
 /* out[o,:] = epilogue(sum_k W[:,k,:] . in[map[k][o],:]).

@@ -45,7 +45,8 @@ int spconvb_conv_forward(const spconvb_conv_params* p, const void* in, const int
     return SPCONVB_E_ARG;
   if (launch_rows == 0 || launch_rows > cap) launch_rows = cap;
   cudaStream_t st = (cudaStream_t)stream;
-  if (!p->force_simt && w_packed && conv_umma_supported(p->compute, p->cin, p->cout))
+  if (!p->force_simt && w_packed && p->kvol <= 27 &&
+      conv_umma_supported(p->compute, p->cin, p->cout))
     return conv_umma_launch(*p, in, map, cap, n_out_ptr, launch_rows, w_packed, scale, bias, out,
                             status, st);
   return conv_simt_launch(*p, in, map, cap, n_out_ptr, launch_rows, w_plain, scale, bias, out,

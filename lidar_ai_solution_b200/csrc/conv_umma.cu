@@ -12,16 +12,18 @@
 //              one output row per thread with 16-byte stores
 //   warp  4    allocates TMEM; one lane issues tcgen05.mma (kind::i8 with int32
 //              accumulators or kind::f16 with fp32 accumulators)
-//   warps 5-8  producers, one thread per tile row: gather the row's
-//              neighbours with 16-byte cp.async (zero-fill for missing ones)
-//              straight into the 128-byte-swizzled K-major layout the MMA
-//              reads; thread 0 also streams the pre-swizzled weight chunk with
-//              one bulk async copy
+//   warps 5-12 producers: prefetch the tile's neighbour indices one tile ahead,
+//              gather the neighbour rows with 16-byte cp.async (8 lanes per
+//              row, so a row is one contiguous request; zero-fill for missing
+//              neighbours) straight into the 128-byte-swizzled K-major layout
+//              the MMA reads, fence the generic-proxy writes for the async
+//              proxy and arrive once per warp; thread 0 also streams the
+//              pre-swizzled weight chunk with one bulk async copy
 //
 // K is walked in chunks of 128 bytes (one swizzle atom per row): a chunk is 8
 // taps of a 16-byte row, ..., 1 tap of a 128-byte row, or half a 256-byte row.
-// Stages cycle through a 4-deep ring guarded by mbarriers; the accumulator is
-// double-buffered in TMEM so the epilogue of tile t overlaps the MMAs of t+1.
+// Stages cycle through a 6- to 8-deep ring guarded by mbarriers; the accumulator
+// is double-buffered in TMEM so the epilogue of tile t overlaps the MMAs of t+1.
 //
 // Every wait is bounded: a wait that runs out sets SPCONVB_ST_TIMEOUT in the
 // status block, raises a CTA-wide abort flag and all roles leave their loops,
@@ -33,15 +35,23 @@ namespace spconvb {
 namespace {
 
 constexpr int kTileM = 128;
-constexpr int kStages = 4;
-constexpr int kLag = 2;  // cp.async groups in flight per producer thread
 constexpr int kChunk = 128;
+constexpr int kMaxTaps = 27;  // taps whose neighbour indices are staged in shared memory
+// Depth of the stage ring: as deep as shared memory allows next to the index
+// staging area, so that enough gather bytes are in flight to cover L2 latency.
+template <int COUT>
+struct Ring {
+  static constexpr int kStages = COUT <= 32 ? 8 : (COUT == 64 ? 7 : 6);
+  // A producer signals a stage "full" kLag chunks after issuing its copies; the
+  // other kStages - kLag stages are slack for the round trip through the MMA.
+  static constexpr int kLag = 2;
+};
 constexpr int kABytes = kTileM * kChunk;
 constexpr int kEpiWarps = 4;
 constexpr int kMmaWarp = 4;
 constexpr int kProdWarp0 = 5;
-constexpr int kProdThreads = 128;
-constexpr int kCtaThreads = 32 * 9;
+constexpr int kProdThreads = 256;
+constexpr int kCtaThreads = 32 * 5 + kProdThreads;
 constexpr unsigned long long kWaitLimitNs = 250ull * 1000 * 1000;
 
 struct UmmaArgs {
@@ -112,7 +122,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
   return mbar_wait_slow(bar, parity, abort_flag, status, where);
 }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src),
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src),
                "r"(src_bytes)
                : "memory");
 }
@@ -196,13 +206,16 @@ __device__ __forceinline__ constexpr uint32_t make_idesc() {
 
 template <int COUT>
 constexpr size_t umma_smem_bytes() {
-  return 1024 + (size_t)kStages * (kABytes + COUT * kChunk) + 256 + 2 * COUT * sizeof(float);
+  return 1024 + (size_t)Ring<COUT>::kStages * (kABytes + COUT * kChunk) +
+         2 * (kMaxTaps + 1) * kTileM * sizeof(int32_t) + 256 + 2 * COUT * sizeof(float);
 }
 
 // ------------------------------------------------------------------- kernel
 template <bool INT8, int RB, int COUT>
 __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArgs a) {
   constexpr int kBBytes = COUT * kChunk;
+  constexpr int kStages = Ring<COUT>::kStages;
+  constexpr int kLag = Ring<COUT>::kLag;
   constexpr uint32_t kTmemCols = (2 * COUT < 32) ? 32 : 2 * COUT;
   constexpr int OPC = RB <= kChunk ? kChunk / RB : 1;   // taps per chunk
   constexpr int SPO = RB <= kChunk ? RB / 16 : 8;       // 16-byte segments per tap per chunk
@@ -215,8 +228,9 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
   uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
   uint8_t* sA = smem;
   uint8_t* sB = sA + kStages * kABytes;
-  uint64_t* bars = (uint64_t*)(sB + kStages * kBBytes);
-  uint32_t* tmem_holder = (uint32_t*)(bars + 2 * kStages + 4);
+  int32_t* sIdx = (int32_t*)(sB + kStages * kBBytes);  // [2][kMaxTaps + 1][kTileM]
+  uint64_t* bars = (uint64_t*)(sIdx + 2 * (kMaxTaps + 1) * kTileM);
+  uint32_t* tmem_holder = (uint32_t*)(bars + 2 * kStages + 6);
   volatile uint32_t* abort_flag = tmem_holder + 1;
   float* s_scale = (float*)(tmem_holder + 4);
   float* s_bias = s_scale + COUT;
@@ -225,19 +239,21 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
   const uint32_t bar_empty = bar_full + 8 * kStages;
   const uint32_t bar_tfull = bar_empty + 8 * kStages;
   const uint32_t bar_tempty = bar_tfull + 16;
+  const uint32_t bar_idx = bar_tempty + 16;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(bar_full + 8 * s, kProdThreads + 1);
+      mbar_init(bar_full + 8 * s, kProdThreads / 32 + 1);
       mbar_init(bar_empty + 8 * s, 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar_tfull + 8 * b, 1);
-      mbar_init(bar_tempty + 8 * b, kEpiWarps * 32);
+      mbar_init(bar_tempty + 8 * b, kEpiWarps);
     }
+    mbar_init(bar_idx, kProdThreads / 32);
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async();
@@ -249,6 +265,8 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
+  for (int i = threadIdx.x; i < 2 * kTileM; i += blockDim.x)
+    sIdx[((i >> 7) * (kMaxTaps + 1) + kMaxTaps) * kTileM + (i & 127)] = -1;
   for (int i = threadIdx.x; i < COUT; i += blockDim.x) {
     s_scale[i] = a.scale ? a.scale[i] : 1.f;
     s_bias[i] = a.bias ? a.bias[i] : 0.f;
@@ -266,25 +284,61 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
 
   if (warp >= kProdWarp0) {
     // ------------------------------------------------------------ producers
+    // A chunk of the A tile is 128 rows x 8 segments of 16 bytes = 1024 copies,
+    // 4 per producer thread.  Lanes run over the segments first (8 lanes per
+    // row), so the lanes that read the same neighbour row ask for one contiguous
+    // piece of it and a warp instruction touches 4..32 cache lines, not always 32.
+    // The code is branch-free (missing neighbours are zero-filled copies) so the
+    // index loads, address arithmetic and copies of the 4 items overlap.
     const uint32_t r = threadIdx.x - kProdWarp0 * 32;
-    const uint32_t rsw = r & 7u;
-    const uint32_t a_row_off = (r >> 3) * 1024u + rsw * 128u;
-    uint32_t it = 0;
-    bool alive = true;
-    for (uint32_t tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x) {
-      const uint32_t row = tile * kTileM + r;
-      const bool valid = row < n_out;
-      const int32_t* mrow = a.map + row;
-      int32_t nxt[OPC];
+    const uint32_t seg = r & 7u;           // 16-byte segment of the chunk this thread copies
+    const uint32_t rb = r >> 3;            // rows rb, rb+32, rb+64, rb+96
+    const uint32_t rsw = rb & 7u;
+    const uint32_t dst_off = (rb >> 3) * 1024u + rsw * 128u + ((seg ^ rsw) << 4);
+    // tap (within the chunk) and byte offset (within the neighbour row) of `seg`
+    const uint32_t seg_tap = RB <= kChunk ? seg / SPO : 0u;
+    const uint32_t seg_byte = RB <= kChunk ? (seg % SPO) * 16u : seg * 16u;
+    // Neighbour indices: thread t fetches taps of parity t/128 of row t%128 into
+    // registers one tile ahead, publishes them in shared memory (double
+    // buffered); the producers meet on an mbarrier before gathering.
+    constexpr int kFetch = (kMaxTaps + 1) / 2;
+    const uint32_t frow = r & 127u, fpar = r >> 7;
+    auto fetch_indices = [&](uint32_t tile, int32_t (&v)[kFetch]) {
+      const uint32_t row = tile * kTileM + frow;
+      const bool valid = tile < ntiles && row < n_out;
+      const int32_t* src = a.map + row;
 #pragma unroll
-      for (int o = 0; o < OPC; ++o) {
-        const int k = o;  // chunk 0
-        nxt[o] = (valid && k < a.kvol) ? __ldg(mrow + (size_t)k * a.cap) : -1;
+      for (int i = 0; i < kFetch; ++i) {
+        const int k = 2 * i + (int)fpar;
+        v[i] = (valid && k < a.kvol) ? __ldg(src + (size_t)k * a.cap) : -1;
+      }
+    };
+    // mbarrier traffic is kept per warp: one lane polls and broadcasts, one lane
+    // arrives after __syncwarp.
+    auto warp_wait = [&](uint32_t bar, uint32_t parity, uint32_t where) -> bool {
+      uint32_t ok = 1u;
+      if (lane == 0) ok = mbar_wait(bar, parity, abort_flag, a.status, where) ? 1u : 0u;
+      return __shfl_sync(0xffffffffu, ok, 0) != 0u;
+    };
+    uint32_t it = 0, lt = 0;
+    bool alive = true;
+    int32_t nxt[kFetch];
+    fetch_indices(blockIdx.x, nxt);
+    for (uint32_t tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x, ++lt) {
+      int32_t* idx = sIdx + (size_t)(lt & 1u) * (kMaxTaps + 1) * kTileM;
+#pragma unroll
+      for (int i = 0; i < kFetch; ++i) idx[(2 * i + fpar) * kTileM + frow] = nxt[i];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_idx);
+      fetch_indices(tile + gridDim.x, nxt);
+      if (!warp_wait(bar_idx, lt & 1u, 5u)) {
+        alive = false;
+        break;
       }
       for (int j = 0; j < nchunk; ++j, ++it) {
         const uint32_t s = it % kStages;
         const uint32_t ph = (it / kStages) & 1u;
-        if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, a.status, 1u)) {
+        if (!warp_wait(bar_empty + 8 * s, ph ^ 1u, 1u)) {
           alive = false;
           break;
         }
@@ -293,40 +347,33 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
           bulk_g2s(smem_u32(sB + s * kBBytes), a.wpk + (size_t)j * kBBytes, kBBytes,
                    bar_full + 8 * s);
         }
-        int32_t cur[OPC];
+        const int k = (RB <= kChunk) ? j * OPC + (int)seg_tap : j / CPT;
+        const uint32_t byte = seg_byte + (RB > kChunk ? (uint32_t)(j % CPT) * kChunk : 0u);
+        // taps beyond kvol read the all -1 row kMaxTaps of the index buffer
+        const int32_t* idx_k = idx + (k < a.kvol ? k : kMaxTaps) * kTileM + rb;
+        const uint32_t dst0 = smem_u32(sA + s * kABytes) + dst_off;
+        int32_t src_row[4];
 #pragma unroll
-        for (int o = 0; o < OPC; ++o) cur[o] = nxt[o];
-        if (j + 1 < nchunk) {
+        for (int i = 0; i < 4; ++i) src_row[i] = idx_k[i * 32];
 #pragma unroll
-          for (int o = 0; o < OPC; ++o) {
-            const int k = (RB <= kChunk) ? (j + 1) * OPC + o : (j + 1) / CPT;
-            nxt[o] = (valid && k < a.kvol) ? __ldg(mrow + (size_t)k * a.cap) : -1;
-          }
-        }
-        const uint32_t dst_row = smem_u32(sA + s * kABytes) + a_row_off;
-#pragma unroll
-        for (int o = 0; o < OPC; ++o) {
-          const int32_t src_row = cur[o];
-          const uint8_t* src = a.in + (size_t)(src_row < 0 ? 0 : src_row) * RB +
-                               (RB > kChunk ? (size_t)(j % CPT) * kChunk : 0);
-          const uint32_t nbytes = src_row < 0 ? 0u : 16u;
-#pragma unroll
-          for (int sg = 0; sg < SPO; ++sg) {
-            const uint32_t c = (uint32_t)(o * SPO + sg);
-            cp_async16(dst_row + ((c ^ rsw) << 4), src + sg * 16, nbytes);
-          }
+        for (int i = 0; i < 4; ++i) {
+          const int32_t sr = src_row[i];
+          cp_async16(dst0 + (uint32_t)i * 4096u, a.in + (size_t)(sr < 0 ? 0 : sr) * RB + byte,
+                     sr < 0 ? 0u : 16u);
         }
         cp_async_commit();
         if (it >= (uint32_t)kLag) {
           cp_async_wait<kLag>();
-          fence_proxy_async();
-          mbar_arrive(bar_full + 8 * ((it - kLag) % kStages));
+          fence_proxy_async();  // generic-proxy writes -> async-proxy reads of the MMA
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_full + 8 * ((it - kLag) % kStages));
         }
       }
     }
     cp_async_wait<0>();
     fence_proxy_async();
-    if (alive) {
+    __syncwarp();
+    if (alive && lane == 0) {
       const uint32_t first = it > (uint32_t)kLag ? it - kLag : 0u;
       for (uint32_t i = first; i < it; ++i) mbar_arrive(bar_full + 8 * (i % kStages));
     }
@@ -369,35 +416,46 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
     uint32_t tl = 0;
     for (uint32_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++tl) {
       const uint32_t buf = tl & 1u;
+      const uint32_t row = tile * kTileM + warp * 32 + lane;
+      // the residual row is fetched before the accumulator is waited for, so its
+      // latency hides behind the tile's MMAs
+      constexpr int kResVecs = COUT / 8;  // 16-byte vectors of an fp16 row (int8: half of them)
+      uint4 rres[kResVecs];
+      if (ep.has_res && row < n_out) {
+        const uint4* rp = (const uint4*)(a.res + (size_t)row * COUT * res_b);
+        const int nv = ep.res_kind == SPCONVB_I8 ? COUT / 16 : COUT / 8;
+#pragma unroll
+        for (int i = 0; i < kResVecs; ++i)
+          if (i < nv) rres[i] = __ldg(rp + i);
+      }
       uint32_t ok = 1u;
       if (lane == 0)
         ok = mbar_wait(bar_tfull + 8 * buf, (tl >> 1) & 1u, abort_flag, a.status, 4u) ? 1u : 0u;
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t row = tile * kTileM + warp * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + buf * COUT;
-#pragma unroll 1
+#pragma unroll
       for (int c0 = 0; c0 < COUT; c0 += 16) {
         uint32_t v[16];
         tmem_ld16(taddr + c0, v);
         tmem_ld_wait();
         if (c0 + 16 == COUT) {
           tc_fence_before();
-          mbar_arrive(bar_tempty + 8 * buf);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
         }
         if (row < n_out) {
           float rdeq[16];
           if (ep.has_res) {
-            const uint8_t* rp = a.res + ((size_t)row * COUT + c0) * res_b;
             if (ep.res_kind == SPCONVB_I8) {
-              const uint4 q = *(const uint4*)rp;
+              const uint4 q = rres[c0 / 16];
               const int8_t* qb = (const int8_t*)&q;
 #pragma unroll
               for (int i = 0; i < 16; ++i) rdeq[i] = __fmul_rn((float)qb[i], ep.res_scale);
             } else {
-              const uint4 q0 = *(const uint4*)rp;
-              const uint4 q1 = *(const uint4*)(rp + 16);
+              const uint4 q0 = rres[(c0 / 8) % kResVecs];
+              const uint4 q1 = rres[(c0 / 8 + 1) % kResVecs];
               const __half* h0 = (const __half*)&q0;
               const __half* h1 = (const __half*)&q1;
 #pragma unroll
@@ -549,6 +607,7 @@ int conv_umma_launch(const spconvb_conv_params& p, const void* in, const int32_t
                      const void* w_packed, const float* scale, const float* bias, void* out,
                      uint32_t* status, cudaStream_t st) {
   if (!w_packed) return SPCONVB_E_ARG;
+  if (p.kvol > kMaxTaps) return SPCONVB_E_UNSUPPORTED;
   if (p.compute == SPCONVB_I8 && !scale) return SPCONVB_E_ARG;
   if (((uintptr_t)in | (uintptr_t)out | (uintptr_t)w_packed | (uintptr_t)p.res) & 15u)
     return SPCONVB_E_ARG;

@@ -270,7 +270,8 @@ int Engine::compile(const Builder& b, int precision, uint32_t build_flags, cudaS
           coordsets[in_cs].bound = n.out_bound;
         // --- input representation
         const bool cout_ok = n.cout == 16 || n.cout == 32 || n.cout == 64 || n.cout == 128;
-        int cpad = (flags & SPCONVB_BUILD_FORCE_SIMT) || !cout_ok ? 0 : padded_cin(compute, n.cin);
+        const bool taps_ok = n.ksize[0] * n.ksize[1] * n.ksize[2] <= 27;
+        int cpad = (flags & SPCONVB_BUILD_FORCE_SIMT) || !cout_ok || !taps_ok ? 0 : padded_cin(compute, n.cin);
         const bool umma = cpad != 0;
         if (!umma) cpad = n.cin;
         float in_scale = 1.f;  // scale of the int8 input actually fed to the MMA

@@ -14,8 +14,7 @@ namespace spconvb {
 
 constexpr int kThreads = 256;
 constexpr int kScanThreads = 1024;
-constexpr int kScanWordsPerThread = 4;
-constexpr int kScanWordsPerBlock = kScanThreads * kScanWordsPerThread;
+constexpr int kScanWordsPerBlock = kScanThreads;  // one bitmap word per thread
 
 // ------------------------------------------------------------------ hash build
 __global__ void hash_build_kernel(const int4* __restrict__ coords, const uint32_t* n_ptr,
@@ -121,16 +120,8 @@ __global__ void down_mark_kernel(const int4* __restrict__ coords, const uint32_t
 // Per block of kScanWordsPerBlock words: exclusive scan of popcounts.
 __global__ void __launch_bounds__(kScanThreads) down_scan_kernel(DownWs ws) {
   __shared__ uint32_t warp_sums[kScanThreads / 32];
-  const uint32_t base = blockIdx.x * kScanWordsPerBlock + threadIdx.x * kScanWordsPerThread;
-  uint32_t cnt[kScanWordsPerThread];
-  uint32_t local = 0;
-#pragma unroll
-  for (int i = 0; i < kScanWordsPerThread; ++i) {
-    uint32_t w = base + i;
-    cnt[i] = w < ws.words ? __popc(ws.bitmap[w]) : 0u;
-    local += cnt[i];
-  }
-  // inclusive warp scan of `local`
+  const uint32_t w = blockIdx.x * kScanWordsPerBlock + threadIdx.x;
+  const uint32_t local = w < ws.words ? __popc(ws.bitmap[w]) : 0u;
   uint32_t incl = local;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
@@ -152,23 +143,17 @@ __global__ void __launch_bounds__(kScanThreads) down_scan_kernel(DownWs ws) {
     if (lane == 31) ws.block_sums[blockIdx.x] = s;
   }
   __syncthreads();
-  uint32_t run = warp_sums[warp] + incl - local;
-#pragma unroll
-  for (int i = 0; i < kScanWordsPerThread; ++i) {
-    uint32_t w = base + i;
-    if (w < ws.words) ws.prefix[w] = run;
-    run += cnt[i];
-  }
+  if (w < ws.words) ws.prefix[w] = warp_sums[warp] + incl - local;
 }
 
-// Ranks every set bit: writes the output coordinate, inserts it in the output
-// hash table, makes the prefix global, and the last block publishes the count.
+// Ranks every set bit (one word per thread, so at most 32 rows each): writes
+// the output coordinate, makes the prefix global, and the last block publishes
+// the count.  No atomics: rows are inserted in the hash table by the map kernel.
 __global__ void __launch_bounds__(kScanThreads)
 down_emit_kernel(DownWs ws, Grid3 gout, int4* __restrict__ out_coords, uint32_t* n_out_ptr,
-                 uint32_t cap_out, uint64_t* out_table, uint32_t out_mask, uint32_t* status) {
+                 uint32_t cap_out, uint32_t* status) {
   __shared__ uint32_t red[32];
   __shared__ uint32_t s_base;
-  // base = sum of block_sums[0, blockIdx.x)
   uint32_t part = 0;
   for (uint32_t i = threadIdx.x; i < blockIdx.x; i += blockDim.x) part += ws.block_sums[i];
 #pragma unroll
@@ -189,36 +174,41 @@ down_emit_kernel(DownWs ws, Grid3 gout, int4* __restrict__ out_coords, uint32_t*
     }
   }
   __syncthreads();
-  const uint32_t base = s_base;
-  const uint32_t w0 = blockIdx.x * kScanWordsPerBlock + threadIdx.x * kScanWordsPerThread;
-#pragma unroll
-  for (int i = 0; i < kScanWordsPerThread; ++i) {
-    uint32_t w = w0 + i;
-    if (w >= ws.words) break;
-    uint32_t bits = ws.bitmap[w];
-    uint32_t row = base + ws.prefix[w];
-    ws.prefix[w] = row;
-    while (bits) {
-      int b = __ffs(bits) - 1;
-      bits &= bits - 1;
-      if (row < cap_out) {
-        uint32_t cell = (w << 5) + b;
-        uint32_t t = cell;
-        int c2 = t % gout.g[2]; t /= gout.g[2];
-        int c1 = t % gout.g[1]; t /= gout.g[1];
-        int c0 = t % gout.g[0]; t /= gout.g[0];
-        out_coords[row] = make_int4((int)t, c0, c1, c2);
-        if (out_table) hash_insert(out_table, out_mask, cell, row, status);
+  const uint32_t w = blockIdx.x * kScanWordsPerBlock + threadIdx.x;
+  if (w >= ws.words) return;
+  uint32_t bits = ws.bitmap[w];
+  uint32_t row = s_base + ws.prefix[w];
+  ws.prefix[w] = row;
+  if (!bits) return;
+  // decode the word's first cell once, then walk the set bits
+  uint32_t t = w << 5;
+  int c2 = t % gout.g[2]; t /= gout.g[2];
+  int c1 = t % gout.g[1]; t /= gout.g[1];
+  int c0 = t % gout.g[0]; t /= gout.g[0];
+  int bq = (int)t;
+  int prev = 0;
+  while (bits) {
+    const int b = __ffs(bits) - 1;
+    bits &= bits - 1;
+    c2 += b - prev;
+    prev = b;
+    while (c2 >= gout.g[2]) {
+      c2 -= gout.g[2];
+      if (++c1 >= gout.g[1]) {
+        c1 = 0;
+        if (++c0 >= gout.g[0]) { c0 = 0; ++bq; }
       }
-      ++row;
     }
+    if (row < cap_out) out_coords[row] = make_int4(bq, c0, c1, c2);
+    ++row;
   }
 }
 
 __global__ void down_map_kernel(const int4* __restrict__ out_coords, const uint32_t* n_out_ptr,
-                                uint32_t cap_out, Grid3 gin, Kernel3 kr, int kvol,
+                                uint32_t cap_out, Grid3 gin, Grid3 gout, Kernel3 kr, int kvol,
                                 const uint64_t* __restrict__ in_table, uint32_t in_mask,
-                                int32_t* __restrict__ map) {
+                                int32_t* __restrict__ map, uint64_t* out_table,
+                                uint32_t out_mask, uint32_t* status) {
   const uint32_t n = min(*n_out_ptr, cap_out);
   const unsigned long long work = (unsigned long long)n * kvol;
   for (unsigned long long idx = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -227,6 +217,9 @@ __global__ void down_map_kernel(const int4* __restrict__ out_coords, const uint3
     const uint32_t row = (uint32_t)(idx - (unsigned long long)k * n);
     const int k2 = k % kr.k[2], k1 = (k / kr.k[2]) % kr.k[1], k0 = k / (kr.k[2] * kr.k[1]);
     int4 c = __ldg(out_coords + row);
+    // the thread of tap 0 also enters the row in the output hash table
+    if (k == 0 && out_table)
+      hash_insert(out_table, out_mask, voxel_key(c.x, c.y, c.z, c.w, gout), row, status);
     int p0 = c.y * kr.s[0] - kr.p[0] + k0 * kr.d[0];
     int p1 = c.z * kr.s[1] - kr.p[1] + k1 * kr.d[1];
     int p2 = c.w * kr.s[2] - kr.p[2] + k2 * kr.d[2];
@@ -401,10 +394,11 @@ int spconvb_down_map(const int32_t* in_coords, const uint32_t* n_in_ptr, uint32_
   down_scan_kernel<<<ws.blocks, kScanThreads, 0, st>>>(ws);
   SPCONVB_LAUNCH_CHECK();
   down_emit_kernel<<<ws.blocks, kScanThreads, 0, st>>>(ws, gout, (int4*)out_coords, n_out_ptr,
-                                                       cap_out, out_table, out_slots - 1, status);
+                                                       cap_out, status);
   SPCONVB_LAUNCH_CHECK();
   down_map_kernel<<<flat_blocks((unsigned long long)cap_out * kvol), kThreads, 0, st>>>(
-      (const int4*)out_coords, n_out_ptr, cap_out, gin, kr, kvol, in_table, in_slots - 1, map);
+      (const int4*)out_coords, n_out_ptr, cap_out, gin, gout, kr, kvol, in_table, in_slots - 1, map,
+      out_table, out_slots - 1, status);
   SPCONVB_LAUNCH_CHECK();
   return SPCONVB_OK;
 }
