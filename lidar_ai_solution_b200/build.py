@@ -44,7 +44,7 @@ def _newer(target: str, deps) -> bool:
 
 
 def _compile(src: str, obj: str, verbose: bool, extra=()):
-    cmd = [_nvcc(), *NVCC_FLAGS, *extra, "-c", src, "-o", obj]
+    cmd = [_nvcc(), *extra, *NVCC_FLAGS, "-c", src, "-o", obj]  # extra include dirs come first
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")
