@@ -97,6 +97,16 @@ SPCONVB_API int spconvb_subm_map(const int32_t* coords, const uint32_t* n_ptr, u
                                  const uint64_t* table, uint32_t slots, int32_t* map,
                                  uint32_t* status, void* stream);
 
+/* Submanifold map of a coordinate set produced by spconvb_down_map: neighbours
+ * are ranked in that call's workspace (its bitmap and popcount prefix, which
+ * must still be intact), so no hash table is needed for these rows. */
+SPCONVB_API int spconvb_subm_map_ranked(const int32_t* coords, const uint32_t* n_ptr,
+                                        uint32_t cap, uint32_t launch_rows,
+                                        const int32_t grid[3], int32_t batch,
+                                        const int32_t ksize[3], const int32_t dilation[3],
+                                        const void* down_workspace, int32_t* map,
+                                        uint32_t* status, void* stream);
+
 /* Output grid of a strided conv along one axis. */
 SPCONVB_API int32_t spconvb_out_extent(int32_t in, int32_t k, int32_t stride, int32_t pad,
                                        int32_t dilation);
@@ -107,8 +117,9 @@ SPCONVB_API size_t spconvb_down_workspace_bytes(const int32_t out_grid[3], int32
 /* Strided sparse conv rulebook.  Produces the unique output coordinates in
  * ascending ((b*G0+c0)*G1+c1)*G2+c2 order, their count (*n_out_ptr, clipped to
  * cap_out, SPCONVB_ST_OVERFLOW on clipping), the map [kvol][cap_out] and, when
- * out_table != NULL, the hash table of the outputs (ready for the next
- * stage's spconvb_subm_map).  `in_table` must hold the inputs. */
+ * out_table != NULL, the hash table of the outputs.  `workspace` keeps the
+ * outputs' bitmap and rank prefix afterwards (see spconvb_subm_map_ranked).
+ * `in_table` / `in_slots` are not used (kept in the signature; may be NULL / 0). */
 SPCONVB_API int spconvb_down_map(const int32_t* in_coords, const uint32_t* n_in_ptr,
                                  uint32_t cap_in, uint32_t launch_rows, const int32_t in_grid[3],
                                  int32_t batch, const int32_t ksize[3], const int32_t stride[3],

@@ -380,29 +380,41 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------ MMA issue
     if (lane == 0) {
+      // The tensor pipe takes one MMA at a time (about M cycles each), and issuing the
+      // next one blocks until it is free.  Everything that is not an MMA therefore sits
+      // between the second-to-last and the last MMA of a chunk, or is short: the next
+      // stage's barrier is probed while the pipe is busy, so that the first MMA of the
+      // next chunk can follow the last one of this chunk without a bubble.
       constexpr uint32_t idesc = make_idesc<INT8, COUT>();
-      uint32_t it = 0, tl = 0;
+      const uint64_t adesc0 = make_smem_desc(smem_u32(sA));
+      const uint64_t bdesc0 = make_smem_desc(smem_u32(sB));
+      uint32_t s = 0, ph = 0, tl = 0;
+      bool ready = false;  // full[s] already seen complete by a probe
       bool alive = true;
       for (uint32_t tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x, ++tl) {
         const uint32_t buf = tl & 1u;
         if (!mbar_wait(bar_tempty + 8 * buf, ((tl >> 1) & 1u) ^ 1u, abort_flag, a.status, 2u))
           break;
-        tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * COUT;
-        for (int j = 0; j < nchunk; ++j, ++it) {
-          const uint32_t s = it % kStages;
-          const uint32_t ph = (it / kStages) & 1u;
-          if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, a.status, 3u)) {
+        for (int j = 0; j < nchunk; ++j) {
+          if (!ready && !mbar_wait(bar_full + 8 * s, ph, abort_flag, a.status, 3u)) {
             alive = false;
             break;
           }
           tc_fence_after();
-          const uint64_t ad = make_smem_desc(smem_u32(sA + s * kABytes));
-          const uint64_t bd = make_smem_desc(smem_u32(sB + s * kBBytes));
+          const uint64_t ad = adesc0 + (uint64_t)(s * (uint32_t)(kABytes >> 4));
+          const uint64_t bd = bdesc0 + (uint64_t)(s * (uint32_t)(kBBytes >> 4));
           const int nk = (j == nchunk - 1) ? last_ksteps : kChunk / 32;
-          for (int ks = 0; ks < nk; ++ks)
+          for (int ks = 0; ks + 1 < nk; ++ks)
             umma<INT8>(d_tmem, ad + 2u * ks, bd + 2u * ks, idesc, (uint32_t)((j | ks) != 0));
+          const uint32_t s1 = s + 1 == (uint32_t)kStages ? 0u : s + 1;
+          const uint32_t ph1 = s1 == 0u ? ph ^ 1u : ph;
+          ready = mbar_try_wait(bar_full + 8 * s1, ph1);
+          umma<INT8>(d_tmem, ad + 2u * (nk - 1), bd + 2u * (nk - 1), idesc,
+                     (uint32_t)((j | (nk - 1)) != 0));
           tc_commit(bar_empty + 8 * s);
+          s = s1;
+          ph = ph1;
         }
         if (alive) tc_commit(bar_tfull + 8 * buf);
       }

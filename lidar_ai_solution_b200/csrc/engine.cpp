@@ -226,7 +226,10 @@ int Engine::compile(const Builder& b, int precision, uint32_t build_flags, cudaS
       r = rt[r].alias_of;
     }
   };
+  // Only the caller's rows need a hash table; rows made by a strided rulebook are
+  // looked up by rank in the bitmap that rulebook leaves behind.
   auto ensure_hash = [&](int cs) {
+    if (!coordsets[cs].external) return;
     coordsets[cs].need_table = true;
     if ((int)hash_emitted.size() <= cs) hash_emitted.resize(cs + 1, 0);
     if (coordsets[cs].external && !hash_emitted[cs]) {
@@ -338,7 +341,7 @@ int Engine::compile(const Builder& b, int precision, uint32_t build_flags, cudaS
             R.ksize[a] = n.ksize[a]; R.stride[a] = n.subm ? 1 : n.stride[a];
             R.pad[a] = n.pad[a]; R.dil[a] = n.dil[a];
           }
-          ensure_hash(in_cs);
+          if (n.subm) ensure_hash(in_cs);
           Step s;
           if (n.subm) {
             R.out_cs = in_cs;
@@ -347,6 +350,7 @@ int Engine::compile(const Builder& b, int precision, uint32_t build_flags, cudaS
           } else {
             CoordSet cs;
             cs.bound = n.out_bound;
+            cs.made_by_rule = (int)rules.size();
             coordsets.push_back(cs);
             R.out_cs = (int)coordsets.size() - 1;
             s.kind = Step::DOWN_MAP;
@@ -770,9 +774,13 @@ int Engine::forward(const void* features, const int32_t* indices, uint32_t cap_r
       case Step::SUBM_MAP: {
         const Rule& R = rules[s.rule];
         const CoordSet& cs = coordsets[R.in_cs];
-        rc = spconvb_subm_map(cs_coords(R.in_cs), cs_n(R.in_cs), coordsets[R.in_cs].cap,
-                              cs_launch(R.in_cs), cs.grid, batch, R.ksize, R.dil, cs.table,
-                              cs.slots, R.map, status, st);
+        if (cs.external)
+          rc = spconvb_subm_map(cs_coords(R.in_cs), cs_n(R.in_cs), coordsets[R.in_cs].cap,
+                                cs_launch(R.in_cs), cs.grid, batch, R.ksize, R.dil, cs.table,
+                                cs.slots, R.map, status, st);
+        else
+          rc = spconvb_subm_map_ranked(cs.coords, cs.n_ptr, cs.cap, cs.cap, cs.grid, batch, R.ksize,
+                                       R.dil, rules[cs.made_by_rule].ws, R.map, status, st);
         last_launches += 1;
         break;
       }

@@ -68,6 +68,7 @@ struct CoordSet {
   bool external = false;     // the engine input: coordinates owned by the caller
   uint32_t bound = 0;        // rows the model says it may hold (output_bound)
   bool need_table = false;
+  int made_by_rule = -1;     // the strided rulebook whose outputs these rows are
   // filled by prepare()
   uint32_t cap = 0;
   int32_t grid[3] = {0, 0, 0};

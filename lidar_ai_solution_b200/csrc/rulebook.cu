@@ -89,32 +89,61 @@ __host__ __device__ inline uint32_t down_words(const int32_t og[3], int batch) {
   return (uint32_t)((cells + 31) / 32);
 }
 
+// Visits the output cells one input row reaches: for every axis only the taps with
+// (c + pad - k*dil) divisible by the stride and inside the output grid survive, so
+// the nest below does ~14 divisions per row instead of 81, and `visit` runs once
+// per (input row, tap) pair of the rulebook.
+template <typename F>
+__device__ __forceinline__ void for_each_output(const int4 c, const Grid3& gout, const Kernel3& kr,
+                                                F visit) {
+  for (int k0 = 0; k0 < kr.k[0]; ++k0) {
+    const int v0 = c.y + kr.p[0] - k0 * kr.d[0];
+    if (v0 < 0 || v0 % kr.s[0]) continue;
+    const int o0 = v0 / kr.s[0];
+    if (o0 >= gout.g[0]) continue;
+    for (int k1 = 0; k1 < kr.k[1]; ++k1) {
+      const int v1 = c.z + kr.p[1] - k1 * kr.d[1];
+      if (v1 < 0 || v1 % kr.s[1]) continue;
+      const int o1 = v1 / kr.s[1];
+      if (o1 >= gout.g[1]) continue;
+      for (int k2 = 0; k2 < kr.k[2]; ++k2) {
+        const int v2 = c.w + kr.p[2] - k2 * kr.d[2];
+        if (v2 < 0 || v2 % kr.s[2]) continue;
+        const int o2 = v2 / kr.s[2];
+        if (o2 >= gout.g[2]) continue;
+        visit((k0 * kr.k[1] + k1) * kr.k[2] + k2, voxel_key(c.x, o0, o1, o2, gout));
+      }
+    }
+  }
+}
+
 __global__ void down_mark_kernel(const int4* __restrict__ coords, const uint32_t* n_ptr,
-                                 uint32_t cap, Grid3 gin, Grid3 gout, Kernel3 kr, int kvol,
+                                 uint32_t cap, Grid3 gin, Grid3 gout, Kernel3 kr,
                                  uint32_t* bitmap) {
   const uint32_t n = min(*n_ptr, cap);
-  const unsigned long long work = (unsigned long long)n * kvol;
-  for (unsigned long long idx = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
-       idx < work; idx += (unsigned long long)gridDim.x * blockDim.x) {
-    const int k = (int)(idx / n);
-    const uint32_t row = (uint32_t)(idx - (unsigned long long)k * n);
-    const int kk[3] = {k / (kr.k[2] * kr.k[1]), (k / kr.k[2]) % kr.k[1], k % kr.k[2]};
-    int4 c = __ldg(coords + row);
+  for (uint32_t row = blockIdx.x * blockDim.x + threadIdx.x; row < n;
+       row += gridDim.x * blockDim.x) {
+    const int4 c = __ldg(coords + row);
     if ((unsigned)c.x >= (unsigned)gin.batch) continue;
-    const int ci[3] = {c.y, c.z, c.w};
-    int o[3];
-    bool ok = true;
-#pragma unroll
-    for (int a = 0; a < 3; ++a) {
-      int v = ci[a] + kr.p[a] - kk[a] * kr.d[a];
-      ok = ok && v >= 0 && (v % kr.s[a]) == 0;
-      o[a] = v / kr.s[a];
-      ok = ok && o[a] < gout.g[a];
-    }
-    if (!ok) continue;
-    uint32_t cell = voxel_key(c.x, o[0], o[1], o[2], gout);
-    atomicOr(bitmap + (cell >> 5), 1u << (cell & 31));
+    for_each_output(c, gout, kr, [&](int, uint32_t cell) {
+      // up to kvol inputs reach the same cell: look before the atomic, most find the bit set
+      const uint32_t bit = 1u << (cell & 31);
+      uint32_t* word = bitmap + (cell >> 5);
+      if (!(*(volatile uint32_t*)word & bit)) atomicOr(word, bit);
+    });
   }
+}
+
+// Row of an output cell from the bitmap and its (global) popcount prefix, -1 if
+// the cell is not an output or lies beyond the capacity.
+__device__ __forceinline__ int32_t rank_lookup(const uint32_t* __restrict__ bitmap,
+                                               const uint32_t* __restrict__ prefix,
+                                               uint32_t cell, uint32_t cap) {
+  const uint32_t bits = __ldg(bitmap + (cell >> 5));
+  const uint32_t b = cell & 31u;
+  if (!((bits >> b) & 1u)) return -1;
+  const uint32_t row = __ldg(prefix + (cell >> 5)) + __popc(bits & ((1u << b) - 1u));
+  return row < cap ? (int32_t)row : -1;
 }
 
 // Per block of kScanWordsPerBlock words: exclusive scan of popcounts.
@@ -147,8 +176,8 @@ __global__ void __launch_bounds__(kScanThreads) down_scan_kernel(DownWs ws) {
 }
 
 // Ranks every set bit (one word per thread, so at most 32 rows each): writes
-// the output coordinate, makes the prefix global, and the last block publishes
-// the count.  No atomics: rows are inserted in the hash table by the map kernel.
+// the output coordinate, makes the prefix global, and the last block publishes the
+// count.  No atomics.
 __global__ void __launch_bounds__(kScanThreads)
 down_emit_kernel(DownWs ws, Grid3 gout, int4* __restrict__ out_coords, uint32_t* n_out_ptr,
                  uint32_t cap_out, uint32_t* status) {
@@ -204,30 +233,85 @@ down_emit_kernel(DownWs ws, Grid3 gout, int4* __restrict__ out_coords, uint32_t*
   }
 }
 
-__global__ void down_map_kernel(const int4* __restrict__ out_coords, const uint32_t* n_out_ptr,
-                                uint32_t cap_out, Grid3 gin, Grid3 gout, Kernel3 kr, int kvol,
-                                const uint64_t* __restrict__ in_table, uint32_t in_mask,
-                                int32_t* __restrict__ map, uint64_t* out_table,
-                                uint32_t out_mask, uint32_t* status) {
+// The map rows of the outputs start as "no input" (-1); the scatter kernel then
+// writes the pairs that exist.  16-byte stores where the row range allows.
+__global__ void map_fill_kernel(const uint32_t* n_out_ptr, uint32_t cap_out, int kvol,
+                                int32_t* __restrict__ map) {
   const uint32_t n = min(*n_out_ptr, cap_out);
+  const uint32_t n4 = (n + 3) / 4;  // int4 groups per tap (cap_out rows are 16-byte aligned
+                                    // only when cap_out % 4 == 0; else fall back to scalars)
+  const bool vec = (cap_out & 3u) == 0 && (((uintptr_t)map) & 15u) == 0;
+  const unsigned long long work = (unsigned long long)kvol * (vec ? n4 : n);
+  for (unsigned long long idx = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
+       idx < work; idx += (unsigned long long)gridDim.x * blockDim.x) {
+    if (vec) {
+      const uint32_t k = (uint32_t)(idx / n4), g4 = (uint32_t)(idx - (unsigned long long)k * n4);
+      ((int4*)(map + (size_t)k * cap_out))[g4] = make_int4(-1, -1, -1, -1);
+    } else {
+      const uint32_t k = (uint32_t)(idx / n), r = (uint32_t)(idx - (unsigned long long)k * n);
+      map[(size_t)k * cap_out + r] = -1;
+    }
+  }
+}
+
+// Input-stationary fill of the output-stationary map: every (input row, tap) pair
+// finds its output row by rank and writes itself there.  One rank query (two
+// cached loads) per existing pair, instead of kvol hash probes per output row.
+__global__ void down_scatter_kernel(const int4* __restrict__ coords, const uint32_t* n_ptr,
+                                    uint32_t cap, Grid3 gin, Grid3 gout, Kernel3 kr, DownWs ws,
+                                    uint32_t cap_out, int32_t* __restrict__ map) {
+  const uint32_t n = min(*n_ptr, cap);
+  for (uint32_t row = blockIdx.x * blockDim.x + threadIdx.x; row < n;
+       row += gridDim.x * blockDim.x) {
+    const int4 c = __ldg(coords + row);
+    if ((unsigned)c.x >= (unsigned)gin.batch) continue;
+    for_each_output(c, gout, kr, [&](int k, uint32_t cell) {
+      const int32_t o = rank_lookup(ws.bitmap, ws.prefix, cell, cap_out);
+      if (o >= 0) map[(size_t)k * cap_out + o] = (int32_t)row;
+    });
+  }
+}
+
+// Optional: the outputs' hash table, for callers that want one.
+__global__ void hash_rows_kernel(const int4* __restrict__ coords, const uint32_t* n_ptr,
+                                 uint32_t cap, Grid3 g, uint64_t* table, uint32_t mask,
+                                 uint32_t* status) {
+  const uint32_t n = min(*n_ptr, cap);
+  for (uint32_t row = blockIdx.x * blockDim.x + threadIdx.x; row < n;
+       row += gridDim.x * blockDim.x) {
+    const int4 c = __ldg(coords + row);
+    hash_insert(table, mask, voxel_key(c.x, c.y, c.z, c.w, g), row, status);
+  }
+}
+
+// Submanifold map of a coordinate set that came out of down_map: neighbours are
+// found by rank in that set's bitmap, no hash table involved.  One thread per
+// (row, tap); the three taps along the last axis hit the same or adjacent words.
+__global__ void subm_ranked_kernel(const int4* __restrict__ coords, const uint32_t* n_ptr,
+                                   uint32_t cap, Grid3 g, Kernel3 kr, int kvol, DownWs ws,
+                                   int32_t* __restrict__ map) {
+  const uint32_t n = min(*n_ptr, cap);
   const unsigned long long work = (unsigned long long)n * kvol;
   for (unsigned long long idx = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
        idx < work; idx += (unsigned long long)gridDim.x * blockDim.x) {
-    const int k = (int)(idx / n);
-    const uint32_t row = (uint32_t)(idx - (unsigned long long)k * n);
+    // consecutive threads take consecutive taps of one row: their cells are neighbours
+    const uint32_t row = (uint32_t)(idx / kvol);
+    const int k = (int)(idx - (unsigned long long)row * kvol);
     const int k2 = k % kr.k[2], k1 = (k / kr.k[2]) % kr.k[1], k0 = k / (kr.k[2] * kr.k[1]);
-    int4 c = __ldg(out_coords + row);
-    // the thread of tap 0 also enters the row in the output hash table
-    if (k == 0 && out_table)
-      hash_insert(out_table, out_mask, voxel_key(c.x, c.y, c.z, c.w, gout), row, status);
-    int p0 = c.y * kr.s[0] - kr.p[0] + k0 * kr.d[0];
-    int p1 = c.z * kr.s[1] - kr.p[1] + k1 * kr.d[1];
-    int p2 = c.w * kr.s[2] - kr.p[2] + k2 * kr.d[2];
+    const int d0 = (k0 - kr.k[0] / 2) * kr.d[0];
+    const int d1 = (k1 - kr.k[1] / 2) * kr.d[1];
+    const int d2 = (k2 - kr.k[2] / 2) * kr.d[2];
     int32_t r = -1;
-    if ((unsigned)p0 < (unsigned)gin.g[0] && (unsigned)p1 < (unsigned)gin.g[1] &&
-        (unsigned)p2 < (unsigned)gin.g[2])
-      r = hash_lookup(in_table, in_mask, voxel_key(c.x, p0, p1, p2, gin));
-    map[(size_t)k * cap_out + row] = r;
+    if ((d0 | d1 | d2) == 0) {
+      r = (int32_t)row;
+    } else {
+      const int4 c = __ldg(coords + row);
+      const int p0 = c.y + d0, p1 = c.z + d1, p2 = c.w + d2;
+      if ((unsigned)p0 < (unsigned)g.g[0] && (unsigned)p1 < (unsigned)g.g[1] &&
+          (unsigned)p2 < (unsigned)g.g[2] && (unsigned)c.x < (unsigned)g.batch)
+        r = rank_lookup(ws.bitmap, ws.prefix, voxel_key(c.x, p0, p1, p2, g), cap);
+    }
+    map[(size_t)k * cap + row] = r;
   }
 }
 
@@ -341,6 +425,36 @@ int spconvb_subm_map(const int32_t* coords, const uint32_t* n_ptr, uint32_t cap,
   return SPCONVB_OK;
 }
 
+int spconvb_subm_map_ranked(const int32_t* coords, const uint32_t* n_ptr, uint32_t cap,
+                            uint32_t launch_rows, const int32_t grid[3], int32_t batch,
+                            const int32_t ksize[3], const int32_t dilation[3],
+                            const void* down_workspace, int32_t* map, uint32_t* status,
+                            void* stream) {
+  (void)status;
+  if (!coords || !n_ptr || !down_workspace || !map || !grid || !ksize || !dilation)
+    return SPCONVB_E_ARG;
+  if (!grid_fits(grid, batch)) return SPCONVB_E_RANGE;
+  Kernel3 kr;
+  for (int a2 = 0; a2 < 3; ++a2) {
+    if (ksize[a2] < 1 || !(ksize[a2] & 1) || dilation[a2] < 1) return SPCONVB_E_ARG;
+    kr.k[a2] = ksize[a2]; kr.d[a2] = dilation[a2]; kr.s[a2] = 1; kr.p[a2] = 0;
+  }
+  const int kvol = ksize[0] * ksize[1] * ksize[2];
+  if (kvol > 65535) return SPCONVB_E_ARG;
+  DownWs ws;
+  ws.words = down_words(grid, batch);
+  ws.blocks = (ws.words + kScanWordsPerBlock - 1) / kScanWordsPerBlock;
+  ws.bitmap = (uint32_t*)down_workspace;
+  ws.prefix = ws.bitmap + ws.words;
+  ws.block_sums = ws.prefix + ws.words;
+  if (launch_rows == 0 || launch_rows > cap) launch_rows = cap;
+  subm_ranked_kernel<<<flat_blocks((unsigned long long)launch_rows * kvol), kThreads, 0,
+                       (cudaStream_t)stream>>>((const int4*)coords, n_ptr, cap,
+                                               make_grid(grid, batch), kr, kvol, ws, map);
+  SPCONVB_LAUNCH_CHECK();
+  return SPCONVB_OK;
+}
+
 size_t spconvb_down_workspace_bytes(const int32_t out_grid[3], int32_t batch) {
   if (!out_grid || !grid_fits(out_grid, batch)) return 0;
   size_t words = down_words(out_grid, batch);
@@ -356,9 +470,10 @@ int spconvb_down_map(const int32_t* in_coords, const uint32_t* n_in_ptr, uint32_
                      int32_t* map, uint64_t* out_table, uint32_t out_slots, uint32_t flags,
                      uint32_t* status, void* stream) {
   if (!in_coords || !n_in_ptr || !in_grid || !ksize || !stride || !pad || !dilation ||
-      !in_table || !workspace || !out_coords || !n_out_ptr || !map)
+      !workspace || !out_coords || !n_out_ptr || !map)
     return SPCONVB_E_ARG;
-  if (in_slots < 2 || (in_slots & (in_slots - 1))) return SPCONVB_E_ARG;
+  (void)in_table;
+  (void)in_slots;
   if (out_table && (out_slots < 2 || (out_slots & (out_slots - 1)) || out_slots < 2ull * cap_out))
     return SPCONVB_E_ARG;
   if (!grid_fits(in_grid, batch)) return SPCONVB_E_RANGE;
@@ -388,17 +503,24 @@ int spconvb_down_map(const int32_t* in_coords, const uint32_t* n_in_ptr, uint32_
   }
   Grid3 gin = make_grid(in_grid, batch), gout = make_grid(og, batch);
   if (launch_rows == 0 || launch_rows > cap_in) launch_rows = cap_in;
-  down_mark_kernel<<<flat_blocks((unsigned long long)launch_rows * kvol), kThreads, 0, st>>>(
-      (const int4*)in_coords, n_in_ptr, cap_in, gin, gout, kr, kvol, ws.bitmap);
+  down_mark_kernel<<<flat_blocks(launch_rows), kThreads, 0, st>>>(
+      (const int4*)in_coords, n_in_ptr, cap_in, gin, gout, kr, ws.bitmap);
   SPCONVB_LAUNCH_CHECK();
   down_scan_kernel<<<ws.blocks, kScanThreads, 0, st>>>(ws);
   SPCONVB_LAUNCH_CHECK();
   down_emit_kernel<<<ws.blocks, kScanThreads, 0, st>>>(ws, gout, (int4*)out_coords, n_out_ptr,
                                                        cap_out, status);
   SPCONVB_LAUNCH_CHECK();
-  down_map_kernel<<<flat_blocks((unsigned long long)cap_out * kvol), kThreads, 0, st>>>(
-      (const int4*)out_coords, n_out_ptr, cap_out, gin, gout, kr, kvol, in_table, in_slots - 1, map,
-      out_table, out_slots - 1, status);
+  map_fill_kernel<<<flat_blocks((unsigned long long)cap_out * kvol / 4 + 1), kThreads, 0, st>>>(
+      n_out_ptr, cap_out, kvol, map);
+  SPCONVB_LAUNCH_CHECK();
+  down_scatter_kernel<<<flat_blocks(launch_rows), kThreads, 0, st>>>(
+      (const int4*)in_coords, n_in_ptr, cap_in, gin, gout, kr, ws, cap_out, map);
+  if (out_table) {
+    SPCONVB_LAUNCH_CHECK();
+    hash_rows_kernel<<<flat_blocks(cap_out), kThreads, 0, st>>>(
+        (const int4*)out_coords, n_out_ptr, cap_out, gout, out_table, out_slots - 1, status);
+  }
   SPCONVB_LAUNCH_CHECK();
   return SPCONVB_OK;
 }

@@ -63,8 +63,10 @@ def out_grid(grid, ksize, stride, pad, dilation=(1, 1, 1)):
 
 
 def down_map(coords, n_ptr, grid, table, ksize, stride, pad, dilation=(1, 1, 1), cap_out=None,
-             batch=1, status=None, want_table=True, launch_rows=0):
-    """Returns (out_coords, n_out_ptr, map, out_table, out_grid)."""
+             batch=1, status=None, want_table=True, launch_rows=0, return_ws=False):
+    """Returns (out_coords, n_out_ptr, map, out_table, out_grid) and, with ``return_ws``,
+    the workspace (bitmap + rank prefix of the outputs) as a sixth item.  ``table`` is not
+    needed any more and may be None."""
     dev = coords.device
     cap_in = coords.shape[0]
     og = out_grid(grid, ksize, stride, pad, dilation)
@@ -80,10 +82,26 @@ def down_map(coords, n_ptr, grid, table, ksize, stride, pad, dilation=(1, 1, 1),
     otab = torch.empty(slots, dtype=torch.int64, device=dev) if want_table else None
     cabi.check(cabi.lib().spconvb_down_map(
         _ptr(coords), _ptr(n_ptr), cap_in, launch_rows, cabi.i3(grid), batch, cabi.i3(ksize),
-        cabi.i3(stride), cabi.i3(pad), cabi.i3(dilation), _ptr(table), table.numel(), _ptr(ws),
+        cabi.i3(stride), cabi.i3(pad), cabi.i3(dilation), _ptr(table),
+        table.numel() if table is not None else 0, _ptr(ws),
         _ptr(oc), _ptr(n_out), cap_out, _ptr(m), _ptr(otab), slots, 0, _ptr(status), _stream()),
         "down_map")
+    if return_ws:
+        return oc, n_out, m, otab, og, ws
     return oc, n_out, m, otab, og
+
+
+def subm_map_ranked(coords, n_ptr, grid, ws, ksize=(3, 3, 3), dilation=(1, 1, 1), batch=1,
+                    status=None, launch_rows=0):
+    """SubM map of rows that came out of ``down_map`` (ranked in its workspace ``ws``)."""
+    cap = coords.shape[0]
+    kvol = int(np.prod(ksize))
+    m = torch.empty((kvol, cap), dtype=torch.int32, device=coords.device)
+    cabi.check(cabi.lib().spconvb_subm_map_ranked(_ptr(coords), _ptr(n_ptr), cap, launch_rows,
+                                                  cabi.i3(grid), batch, cabi.i3(ksize),
+                                                  cabi.i3(dilation), _ptr(ws), _ptr(m),
+                                                  _ptr(status), _stream()), "subm_map_ranked")
+    return m
 
 
 class ConvWeights:

@@ -86,13 +86,22 @@ def test_hash_reports_duplicates_and_range():
 
 
 def _chain(coords, grid):
+    """Stage 0 looks neighbours up in the hash table of the caller's rows; later stages rank
+    them in the bitmap the strided rulebook left behind (no hash table)."""
     ops = _ops()
     dc, n_ptr, st = _dev(coords), ops.device_count(len(coords)), ops.new_status()
     table = ops.hash_build(dc, n_ptr, grid, status=st)
+    ws = None
     out = []
     for k, s, p in STAGES:
-        m = ops.subm_map(dc, n_ptr, grid, table, status=st)
-        oc, n_out, dm, otab, og = ops.down_map(dc, n_ptr, grid, table, k, s, p, status=st)
+        if ws is None:
+            m = ops.subm_map(dc, n_ptr, grid, table, status=st)
+        else:
+            m = ops.subm_map_ranked(dc, n_ptr, grid, ws, status=st)
+            by_hash = ops.subm_map(dc, n_ptr, grid, table, status=st)
+            assert torch.equal(m[:, : int(n_ptr.item())], by_hash[:, : int(n_ptr.item())])
+        oc, n_out, dm, otab, og, ws = ops.down_map(dc, n_ptr, grid, None, k, s, p, status=st,
+                                                   return_ws=True)
         torch.cuda.synchronize()
         _status_ok(st)
         out.append((dc, n_ptr, list(grid), m, oc, n_out, dm, og))
