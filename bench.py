@@ -186,7 +186,7 @@ def run_reference(args, rank, world):
     cores = orc.num_threads()
     line = {
         "impl": "reference", "metric": "centerpoint_scn_int8_frames_per_s", "value": fps,
-        "unit": "frames/s", "n_gpus": 0, "steps": steps, "warmup": warm,
+        "unit": "frames/s", "n_gpus": args.gpus, "steps": steps, "warmup": warm,
         "ms_per_step": 1000.0 * dt / steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "int8", "data": "synthetic",
         "config": {"workload": WORKLOAD, "frames_per_step": 1, "voxels_per_frame": VOXELS},
@@ -322,9 +322,9 @@ def run_gpu(args, rank, world, local_rank):
         "config": {"workload": WORKLOAD, "frames_per_gpu_per_step": F, "replicas_per_gpu": R,
                    "voxels_per_frame": voxels_per_frame, "parallelism": "frames sharded, no collective",
                    "l2": "no flush: a step touches ~%d MB per GPU (> 126 MB L2)" % (F * 150)},
-        "e2e": {"value": e2e_value, "unit": "frames/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / args.steps},
-        "gpu_launches": launches_per_frame * F * args.steps,
+        "e2e": {"value": e2e_value, "unit": "frames/s", "h2d_bytes_per_step": h2d * world,
+                "d2h_bytes_per_step": d2h * world, "ms_per_step": ms_e2e / args.steps},
+        "gpu_launches": launches_per_frame * F * args.steps * world,
         "active_voxels_per_s": value * voxels_per_frame,
         "clocks": clocks,
     }
@@ -405,9 +405,12 @@ def run_gpu(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
-# DRAM bytes (read + write) of the convolution launches of one frame, from the
-# ncu capture summarised in profiles/; None until a capture has been made.
-CONV_DRAM_TRAFFIC_PER_FRAME = None
+# DRAM bytes (read + write) of the convolution launches of one frame.  ncu cannot
+# capture the full frame within its size limits, so this scales one captured launch
+# (profiles/conv_umma_int8_c64_170k.md: dram read + write = 29.43 MB for 40.23 MB of
+# algorithmic bytes; the output is still in L2 when the launch ends) to the frame's
+# 704.4 MB of algorithmic convolution bytes, traffic growing in proportion to rows.
+CONV_DRAM_TRAFFIC_PER_FRAME = 0.7316 * 704387816
 
 
 def main():
