@@ -113,10 +113,31 @@ def make_frames(count, seed0, voxels=VOXELS):
     return frames
 
 
-def build_int8_model(torch):
-    """Random-init CenterPoint SCN, activation ranges from absmax on the seed-0 frame."""
+# Workloads: the default is the one the headline metric is quoted on; the others are the
+# remaining benchmark configurations, selectable for extra measurements.
+WORKLOADS = {
+    "centerpoint_int8": dict(kind="centerpoint", precision="int8", voxels=(VOXELS, VOXELS),
+                             bound=OUTPUT_BOUND, name=WORKLOAD),
+    "centerpoint_int8_mixed": dict(
+        kind="centerpoint", precision="int8", voxels=(60000, 200000), bound=520000,
+        name="centerpoint_scn_int8 full backbone, 41x1440x1440 grid, voxel counts U[60k,200k]"),
+    "bevfusion_fp16": dict(
+        kind="bevfusion", precision="fp16", voxels=(VOXELS, VOXELS), bound=OUTPUT_BOUND,
+        name="bevfusion lidar SparseEncoder fp16, 41x1440x1440 grid, ~120k active voxels/frame"),
+}
+
+
+def frame_voxels(spec, seed):
+    lo, hi = spec["voxels"]
+    return lo if lo == hi else int(np.random.default_rng(seed).integers(lo, hi + 1))
+
+
+def build_model(torch, spec):
+    """Random-init backbone; for int8, activation ranges from absmax on the seed-0 frame."""
     from lidar_ai_solution_b200 import engine, models, scenes
-    model = models.scn_backbone("centerpoint", seed=0, grid_zyx=GRID, output_bound=OUTPUT_BOUND)
+    model = models.scn_backbone(spec["kind"], seed=0, grid_zyx=GRID, output_bound=spec["bound"])
+    if spec["precision"] != "int8":
+        return model
     coords = scenes.make_coords(VOXELS, GRID, 0)
     feats = scenes.make_point_features(coords, 0)
     ranges = engine.calibrate(model, torch.from_numpy(feats).cuda(),
@@ -166,35 +187,39 @@ def run_reference(args, rank, world):
         return
     from lidar_ai_solution_b200 import models, scenes
     from oracle import graph_oracle, oracle as orc
-    model = models.scn_backbone("centerpoint", seed=0, grid_zyx=GRID, output_bound=OUTPUT_BOUND)
-    coords = scenes.make_coords(VOXELS, GRID, 0)
-    feats = scenes.make_point_features(coords, 0)
-    # calibration on the CPU: fp16 run of the seed frame, absmax per tensor
-    _, T = graph_oracle.run(model, feats, coords, GRID, "fp16")
-    ranges = {k: float(np.abs(v["feat"].astype(np.float32)).max()) for k, v in T.items()}
-    qm = models.quantize(model, ranges)
+    spec = WORKLOADS[args.workload]
+    qm = models.scn_backbone(spec["kind"], seed=0, grid_zyx=GRID, output_bound=spec["bound"])
+    if spec["precision"] == "int8":
+        coords = scenes.make_coords(VOXELS, GRID, 0)
+        feats = scenes.make_point_features(coords, 0)
+        # calibration on the CPU: fp16 run of the seed frame, absmax per tensor
+        _, T = graph_oracle.run(qm, feats, coords, GRID, "fp16")
+        ranges = {k: float(np.abs(v["feat"].astype(np.float32)).max()) for k, v in T.items()}
+        qm = models.quantize(qm, ranges)
     steps = max(1, min(args.steps, 6))
     warm = max(0, min(args.warmup, 1))
-    frames = make_frames(steps + warm, 1)
+    frames = [make_frames(1, s, frame_voxels(spec, s))[0] for s in range(1, 1 + steps + warm)]
     for f, c in frames[:warm]:
-        graph_oracle.run(qm, f, c, GRID, "int8")
+        graph_oracle.run(qm, f, c, GRID, spec["precision"])
     t0 = time.perf_counter()
     for f, c in frames[warm:]:
-        graph_oracle.run(qm, f, c, GRID, "int8")
+        graph_oracle.run(qm, f, c, GRID, spec["precision"])
     dt = time.perf_counter() - t0
+    voxels = float(np.mean([len(f) for f, _ in frames[warm:]]))
     fps = steps / dt
     cores = orc.num_threads()
     line = {
-        "impl": "reference", "metric": "centerpoint_scn_int8_frames_per_s", "value": fps,
+        "impl": "reference",
+        "metric": "%s_scn_%s_frames_per_s" % (spec["kind"], spec["precision"]), "value": fps,
         "unit": "frames/s", "n_gpus": args.gpus, "steps": steps, "warmup": warm,
         "ms_per_step": 1000.0 * dt / steps, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "frames_per_step": 1, "voxels_per_frame": VOXELS},
+        "vs_baseline": None, "dtype": spec["precision"], "data": "synthetic",
+        "config": {"workload": spec["name"], "frames_per_step": 1, "voxels_per_frame": voxels},
         "cpu_baseline": {"value": fps, "unit": "frames/s", "cores": cores, "kind": "port",
                          "sample": "%d frames, one per step, all host threads (OpenMP)" % steps},
         "e2e": {"value": fps, "unit": "frames/s", "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
-        "active_voxels_per_s": fps * VOXELS,
+        "active_voxels_per_s": fps * voxels,
     }
     print(json.dumps(line), flush=True)
 
@@ -213,16 +238,17 @@ def run_gpu(args, rank, world, local_rank):
         dist.init_process_group("nccl", device_id=dev)
     cabi.lib()  # fails loudly if the CUDA extension was not built
 
-    qm = build_int8_model(torch)
+    spec = WORKLOADS[args.workload]
+    precision = engine.PRECISION_INT8 if spec["precision"] == "int8" else engine.PRECISION_FP16
+    qm = build_model(torch, spec)
     tmp = tempfile.mkdtemp(prefix="scn_bench_")
-    onnx_path = os.path.join(tmp, "centerpoint.scn.PTQ.onnx")
+    onnx_path = os.path.join(tmp, "model.scn.onnx")
     onnx_writer.save(qm, onnx_path)
 
     F, R = args.frames, max(1, min(args.replicas, args.frames))
-    frames = [make_frames(1, s)[0] for s in sharding.frame_seeds(rank, F)]
+    frames = [make_frames(1, s, frame_voxels(spec, s))[0] for s in sharding.frame_seeds(rank, F)]
     streams = [torch.cuda.Stream(device=dev) for _ in range(R)]
-    engines = [engine.Engine.from_onnx(onnx_path, engine.PRECISION_INT8, 0, 0, dev)
-               for _ in range(R)]
+    engines = [engine.Engine.from_onnx(onnx_path, precision, 0, 0, dev) for _ in range(R)]
     for e in engines:
         e.prepare(GRID)
 
@@ -315,11 +341,12 @@ def run_gpu(args, rank, world, local_rank):
     d2h = out_bytes * F
 
     line = {
-        "metric": "centerpoint_scn_int8_frames_per_s", "value": value, "unit": "frames/s",
+        "metric": "%s_scn_%s_frames_per_s" % (spec["kind"], spec["precision"]), "value": value,
+        "unit": "frames/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "frames_per_gpu_per_step": F, "replicas_per_gpu": R,
+        "vs_baseline": None, "dtype": spec["precision"], "data": "synthetic",
+        "config": {"workload": spec["name"], "frames_per_gpu_per_step": F, "replicas_per_gpu": R,
                    "voxels_per_frame": voxels_per_frame, "parallelism": "frames sharded, no collective",
                    "l2": "no flush: a step touches ~%d MB per GPU (> 126 MB L2)" % (F * 150)},
         "e2e": {"value": e2e_value, "unit": "frames/s", "h2d_bytes_per_step": h2d * world,
@@ -331,7 +358,7 @@ def run_gpu(args, rank, world, local_rank):
 
     if rank == 0:
         # ---- per-kernel times (cold L2) and the roofline of the dominant kernel
-        prof_engine = engine.Engine.from_onnx(onnx_path, engine.PRECISION_INT8, 0, 0, dev)
+        prof_engine = engine.Engine.from_onnx(onnx_path, precision, 0, 0, dev)
         flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
         prof_engine.forward(dev_f[0], dev_c[0], GRID)
         torch.cuda.synchronize()
@@ -363,7 +390,7 @@ def run_gpu(args, rank, world, local_rank):
             "bound": "hbm", "kernel": "conv_umma_kernel (all %d convolution launches of a frame)" % n_conv,
             "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
             "peak_source": "measured" if "hbm_gbs" in peaks else "fallback",
-            "traffic": CONV_DRAM_TRAFFIC_PER_FRAME,
+            "traffic": CONV_DRAM_PER_ALGORITHMIC_BYTE * conv_bytes,
             "algorithmic_bytes_per_frame": conv_bytes, "kernel_ms_per_frame": conv_ms,
             "share_of_frame_kernel_time": conv_ms / all_ms if all_ms else None,
             "int8_tops_achieved": conv_ops / (conv_ms / 1000.0) / 1e12 if conv_ms else 0.0,
@@ -387,10 +414,11 @@ def run_gpu(args, rank, world, local_rank):
         if world == 1 and not args.no_cpu_baseline:
             from oracle import graph_oracle, oracle as orc
             sample = frames[: max(1, min(args.cpu_frames, F))]
-            graph_oracle.run(qm, sample[0][0][:2000], sample[0][1][:2000], GRID, "int8")  # warm
+            graph_oracle.run(qm, sample[0][0][:2000], sample[0][1][:2000], GRID,
+                             spec["precision"])  # warm
             t0 = time.perf_counter()
             for f, c in sample:
-                graph_oracle.run(qm, f, c, GRID, "int8")
+                graph_oracle.run(qm, f, c, GRID, spec["precision"])
             dt = time.perf_counter() - t0
             line["cpu_baseline"] = {
                 "value": len(sample) / dt, "unit": "frames/s", "cores": orc.num_threads(),
@@ -405,12 +433,13 @@ def run_gpu(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
-# DRAM bytes (read + write) of the convolution launches of one frame.  ncu cannot
-# capture the full frame within its size limits, so this scales one captured launch
-# (profiles/conv_umma_int8_c64_170k.md: dram read + write = 29.43 MB for 40.23 MB of
-# algorithmic bytes; the output is still in L2 when the launch ends) to the frame's
-# 704.4 MB of algorithmic convolution bytes, traffic growing in proportion to rows.
-CONV_DRAM_TRAFFIC_PER_FRAME = 0.7316 * 704387816
+# DRAM bytes (read + write) of the convolution launches per algorithmic byte.  ncu cannot
+# capture the full frame within its size limits, so the frame's traffic is one captured
+# launch (profiles/conv_umma_int8_c64_170k.md: dram read + write = 29.43 MB for 40.23 MB of
+# algorithmic bytes; the output is still in L2 when the launch ends) scaled to the frame's
+# algorithmic convolution bytes (704.4 MB on the default workload), traffic growing in
+# proportion to rows.
+CONV_DRAM_PER_ALGORITHMIC_BYTE = 0.7316
 
 
 def main():
@@ -419,6 +448,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="centerpoint_int8", choices=sorted(WORKLOADS))
     ap.add_argument("--frames", type=int, default=16, help="frames per GPU per step")
     ap.add_argument("--replicas", type=int, default=4, help="engine replicas (streams) per GPU")
     ap.add_argument("--cpu-frames", type=int, default=4, help="frames timed on the CPU oracle")

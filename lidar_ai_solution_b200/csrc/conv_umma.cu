@@ -182,6 +182,15 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
       : "r"(taddr)
       : "memory");
 }
+// float -> int8 value: round to nearest even, saturate to [-128, 127] (one convert).
+__device__ __forceinline__ int cvt_sat_s8(float x) {
+  int q;
+  asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q) : "f"(x));
+  return q;
+}
+__device__ __forceinline__ uint32_t pack_s8x4(int a, int b, int c, int d) {
+  return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
+}
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -458,13 +467,36 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
           if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
         }
         if (row < n_out) {
-          float rdeq[16];
+          // Same arithmetic as common.cuh:epilogue_value, written so that the per-element
+          // work is a handful of instructions: vector loads of scale and bias, ReLU as a
+          // max with 0 or -inf, float -> int8 as one saturating round-to-nearest-even
+          // convert, and the layer-wide switches hoisted out of the element loops.
+          float y[16];
+          const float lo = ep.act == SPCONVB_ACT_RELU ? 0.f : -INFINITY;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const float4 bi = ((const float4*)(s_bias + c0))[g];
+            if (INT8) {
+              const float4 sc = ((const float4*)(s_scale + c0))[g];
+              y[4 * g + 0] = fmaxf(fmaf((float)(int)v[4 * g + 0], sc.x, bi.x), lo);
+              y[4 * g + 1] = fmaxf(fmaf((float)(int)v[4 * g + 1], sc.y, bi.y), lo);
+              y[4 * g + 2] = fmaxf(fmaf((float)(int)v[4 * g + 2], sc.z, bi.z), lo);
+              y[4 * g + 3] = fmaxf(fmaf((float)(int)v[4 * g + 3], sc.w, bi.w), lo);
+            } else {
+              y[4 * g + 0] = fmaxf(__fadd_rn(__uint_as_float(v[4 * g + 0]), bi.x), lo);
+              y[4 * g + 1] = fmaxf(__fadd_rn(__uint_as_float(v[4 * g + 1]), bi.y), lo);
+              y[4 * g + 2] = fmaxf(__fadd_rn(__uint_as_float(v[4 * g + 2]), bi.z), lo);
+              y[4 * g + 3] = fmaxf(__fadd_rn(__uint_as_float(v[4 * g + 3]), bi.w), lo);
+            }
+          }
           if (ep.has_res) {
+            // the conv result as it would have been stored (mid), plus the residual
+            float r[16];
             if (ep.res_kind == SPCONVB_I8) {
               const uint4 q = rres[c0 / 16];
               const int8_t* qb = (const int8_t*)&q;
 #pragma unroll
-              for (int i = 0; i < 16; ++i) rdeq[i] = __fmul_rn((float)qb[i], ep.res_scale);
+              for (int i = 0; i < 16; ++i) r[i] = __fmul_rn((float)qb[i], ep.res_scale);
             } else {
               const uint4 q0 = rres[(c0 / 8) % kResVecs];
               const uint4 q1 = rres[(c0 / 8 + 1) % kResVecs];
@@ -472,34 +504,33 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
               const __half* h1 = (const __half*)&q1;
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
-                rdeq[i] = __half2float(h0[i]);
-                rdeq[8 + i] = __half2float(h1[i]);
+                r[i] = __half2float(h0[i]);
+                r[8 + i] = __half2float(h1[i]);
               }
             }
-          } else {
+            const float lo2 = ep.res_relu ? 0.f : -INFINITY;
+            if (ep.mid_kind == SPCONVB_I8) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) rdeq[i] = 0.f;
-          }
-          float y[16];
+              for (int i = 0; i < 16; ++i) {
+                const float m = __fmul_rn((float)cvt_sat_s8(__fmul_rn(y[i], ep.mid_inv_scale)),
+                                          ep.mid_scale);
+                y[i] = fmaxf(__fadd_rn(m, r[i]), lo2);
+              }
+            } else {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            float t;
-            if (INT8)
-              t = fmaf((float)(int)v[i], s_scale[c0 + i], s_bias[c0 + i]);
-            else
-              t = __fadd_rn(__uint_as_float(v[i]), s_bias[c0 + i]);
-            y[i] = epilogue_value(t, ep, rdeq[i]);
+              for (int i = 0; i < 16; ++i)
+                y[i] = fmaxf(__fadd_rn(__half2float(__float2half_rn(y[i])), r[i]), lo2);
+            }
           }
           uint8_t* op = a.out + ((size_t)row * COUT + c0) * out_b;
           if (ep.out_kind == SPCONVB_I8) {
             uint32_t w[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              w[i] = ((uint32_t)(uint8_t)(int8_t)(int)y[4 * i + 0]) |
-                     ((uint32_t)(uint8_t)(int8_t)(int)y[4 * i + 1] << 8) |
-                     ((uint32_t)(uint8_t)(int8_t)(int)y[4 * i + 2] << 16) |
-                     ((uint32_t)(uint8_t)(int8_t)(int)y[4 * i + 3] << 24);
-            }
+            for (int i = 0; i < 4; ++i)
+              w[i] = pack_s8x4(cvt_sat_s8(__fmul_rn(y[4 * i + 0], ep.inv_out_scale)),
+                               cvt_sat_s8(__fmul_rn(y[4 * i + 1], ep.inv_out_scale)),
+                               cvt_sat_s8(__fmul_rn(y[4 * i + 2], ep.inv_out_scale)),
+                               cvt_sat_s8(__fmul_rn(y[4 * i + 3], ep.inv_out_scale)));
             *(uint4*)op = make_uint4(w[0], w[1], w[2], w[3]);
           } else {
             uint32_t w[8];
