@@ -205,6 +205,16 @@ def test_conv_int8_ragged_row_counts(n):
     assert np.array_equal(got, ref)
 
 
+@pytest.mark.parametrize("n", [1, 3, 255, 256, 257, 511, 513])
+@pytest.mark.parametrize("out_kind", ["i8", "f16"])
+def test_conv_int8_ragged_row_counts_wide_outputs(n, out_kind):
+    """Cout >= 64 runs the kernel variant with 256-row tiles: partial tiles, partial
+    groups of 4 rows in the transposing epilogue, single-row inputs."""
+    kind = orc.KIND_I8 if out_kind == "i8" else orc.KIND_F16
+    got, ref = _int8_layer(n, 32, 64, seed=100 + n, simt=False, out_kind=kind, grid=(7, 11, 13))
+    assert np.array_equal(got.view(np.uint8), ref.view(np.uint8))
+
+
 def _f16_problem(n, cin, cout, seed, grid=(41, 180, 180), kvol=27):
     rng = np.random.default_rng(seed)
     coords = scenes.make_coords(n, grid, seed)
@@ -256,6 +266,40 @@ def test_conv_fp16_cuda_core_bit_exact_and_first_layer_padding():
     _status_ok(st)
     r32 = ref.astype(np.float32)
     assert float(np.abs(tc.cpu().numpy().astype(np.float32) - r32).max()) <= 1e-2 * np.abs(r32).max()
+
+
+@pytest.mark.parametrize("c,n", [(16, 5000), (32, 5001), (64, 5000), (64, 4999), (128, 2050)])
+@pytest.mark.parametrize("res_kind", ["i8", "f16"])
+def test_conv_int8_fused_residual_all_widths(c, n, res_kind):
+    """Fused conv + Add&ReLU == oracle conv (stored int8) followed by oracle add, for both
+    kernel variants (Cout < 64 and >= 64), int8 and fp16 residual operands, row counts
+    that leave partial tiles."""
+    ops = _ops()
+    grid = (41, 180, 180)
+    pb = int8_problem(n, c, c, grid, seed=40 + c)
+    m_ref, _ = orc.subm_map(pb["coords"], grid)
+    rng = np.random.default_rng(6)
+    if res_kind == "i8":
+        res, res_scale = rng.integers(-128, 128, (n, c)).astype(np.int8), 0.031
+    else:
+        res, res_scale = (rng.standard_normal((n, c)) * 2).astype(np.float16), 1.0
+    mid_dr, out_dr = 3.0, 4.5
+    mid = orc.conv_i8(pb["xq"], m_ref, n, pb["wq"], pb["scale"], pb["bias"], orc.ACT_NONE,
+                      orc.KIND_I8, float(np.float32(127.0) / np.float32(mid_dr)))
+    ref = orc.add(mid, float(np.float32(mid_dr) / np.float32(127.0)), res, res_scale, True,
+                  orc.KIND_I8, float(np.float32(127.0) / np.float32(out_dr)))
+    wts = ops.ConvWeights(pb["wq"], ops.I8, pb["scale"], pb["bias"])
+    st = ops.new_status()
+    out = ops.conv_forward(_dev(pb["xq"]), _dev(m_ref), ops.device_count(n), wts,
+                           act=ops.ACT_NONE, out_kind=ops.I8,
+                           inv_out_scale=float(np.float32(127.0) / np.float32(out_dr)),
+                           res=_dev(res), res_scale=res_scale, mid_kind=ops.I8,
+                           mid_inv_scale=float(np.float32(127.0) / np.float32(mid_dr)),
+                           mid_scale=float(np.float32(mid_dr) / np.float32(127.0)),
+                           res_relu=True, status=st)
+    torch.cuda.synchronize()
+    _status_ok(st)
+    assert np.array_equal(out.cpu().numpy(), ref)
 
 
 @pytest.mark.parametrize("simt", [False, True])
