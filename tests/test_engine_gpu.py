@@ -319,3 +319,57 @@ def test_reference_frame_full_size_int8(golden_dir):
     torch.cuda.synchronize()
     assert exact.status()[0] == 0
     assert np.array_equal(exact.output(0).cpu().numpy().view(np.uint16), outs[0].view(np.uint16))
+
+
+# ------------------------------------------------------------ pyscn binding, infer CLI
+def test_pyscn_model_matches_engine(tmp_path):
+    """SCNModel(onnx, precision).forward(features, indices, grid, stream) (pyscn.cpp:47-146):
+    host arrays in and out, same bits as the device-tensor Engine path."""
+    from lidar_ai_solution_b200 import engine, models, onnx_writer, pyscn, scenes
+    grid = (41, 360, 360)
+    model = models.scn_backbone("centerpoint", seed=3, grid_zyx=grid, output_bound=60000)
+    path = str(tmp_path / "m.scn.onnx")
+    onnx_writer.save(model, path)
+    coords = scenes.make_coords(9000, grid, 4)
+    feats = scenes.make_point_features(coords, 4)
+    m = pyscn.SCNModel(path, "fp16")
+    assert m.valid()
+    out, idx = m.forward(feats, coords, list(grid), 0)
+    out2, _ = m.forward(feats, coords, list(grid), torch.cuda.current_stream().cuda_stream)
+    e = engine.Engine.from_onnx(path, engine.PRECISION_FP16)
+    e.forward(torch.from_numpy(feats).cuda(), torch.from_numpy(coords).cuda(), grid)
+    torch.cuda.synchronize()
+    ref = e.output(0).cpu().numpy()
+    assert out.dtype == np.float16 and out.shape == ref.shape and idx.shape == (0, 4)
+    assert np.array_equal(out.view(np.uint16), ref.view(np.uint16))
+    assert np.array_equal(out2.view(np.uint16), ref.view(np.uint16))
+    assert not pyscn.SCNModel(str(tmp_path / "missing.onnx"), "fp16").valid()
+
+
+def test_infer_cli_runs_every_mode(tmp_path, capsys):
+    """The CLI of src/infer.cpp: plain run saves outputN.tensor; cudagraph + dds + profiling
+    prints a latency; stress shrinks the row count under a captured graph; the search lists
+    configurations.  Files use the reference's tensor format."""
+    from lidar_ai_solution_b200 import infer, models, onnx_writer, scenes, tensor_file
+    grid = (41, 360, 360)
+    model = models.scn_backbone("centerpoint", seed=5, grid_zyx=grid, output_bound=60000)
+    onnx = str(tmp_path / "m.scn.onnx")
+    onnx_writer.save(model, onnx)
+    coords = scenes.make_coords(8000, grid, 6)
+    tensor_file.save(scenes.make_point_features(coords, 6), tmp_path / "f.tensor")
+    tensor_file.save(coords, tmp_path / "i.tensor")
+    base = ["--onnx", onnx, "--feature", str(tmp_path / "f.tensor"), "--indice",
+            str(tmp_path / "i.tensor"), "--grid_size", "41,360,360", "--save_dir", str(tmp_path)]
+    assert infer.main(base) == 0
+    plain = tensor_file.load(tmp_path / "output0.tensor")
+    assert plain.dtype == np.float16 and plain.ndim == 4 and np.abs(plain.astype(np.float32)).sum() > 0
+    os.remove(tmp_path / "output0.tensor")
+    assert infer.main(base + ["--cudagraph", "--dds"]) == 0
+    graphed = tensor_file.load(tmp_path / "output0.tensor")
+    assert np.array_equal(plain.view(np.uint16), graphed.view(np.uint16))
+    assert infer.main(base + ["--cudagraph", "--dds", "--profiling"]) == 0
+    assert "Latency:" in capsys.readouterr().out
+    assert infer.main(base + ["--cudagraph", "--stress"]) == 0
+    assert "Stress test done:" in capsys.readouterr().out
+    assert infer.main(base + ["--search_best_perf"]) == 0
+    assert "Best configuration found" in capsys.readouterr().out

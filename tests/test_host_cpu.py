@@ -175,3 +175,47 @@ def test_two_rank_aggregation_over_gloo(tmp_path):
         out, _ = p.communicate(timeout=180)
         assert p.returncode == 0, out
         assert "rank %d ok" % rank in out
+
+
+# ------------------------------------------------------------------ tensor files, CLI
+def test_tensor_file_round_trip_matches_reference_bytes(tmp_path):
+    """tool/tensor.py:24-69: header of three int32, int32 dims, raw data; a file written
+    here must be byte-identical to the fixture written in that format."""
+    from lidar_ai_solution_b200 import tensor_file
+    golden = os.path.join(os.path.dirname(__file__), "golden", "sample.tensor")
+    a = tensor_file.load(golden)
+    assert a.shape == (40, 5) and a.dtype == np.float16
+    out = tmp_path / "x.tensor"
+    tensor_file.save(a, out)
+    assert open(out, "rb").read() == open(golden, "rb").read()
+    for dt in (np.int32, np.float32, np.int8, np.uint8, np.int64):
+        x = (np.arange(24).reshape(2, 3, 4) % 100).astype(dt)
+        tensor_file.save(x, out)
+        y = tensor_file.load(out)
+        assert y.dtype == dt and np.array_equal(x, y)
+
+
+def test_tensor_file_rejects_bad_files(tmp_path):
+    from lidar_ai_solution_b200 import tensor_file
+    bad = tmp_path / "bad.tensor"
+    bad.write_bytes(b"\x00" * 32)
+    with pytest.raises(RuntimeError):
+        tensor_file.load(bad)
+    bad.write_bytes(np.array([0x33FF1101, 2, 2, 4, 4], np.int32).tobytes() + b"\x00" * 8)
+    with pytest.raises(RuntimeError):
+        tensor_file.load(bad)  # truncated data
+    with pytest.raises(RuntimeError):
+        tensor_file.save(np.zeros(3, np.complex64), bad)
+
+
+def test_infer_cli_options_follow_the_reference():
+    """Option names and defaults of src/infer.cpp:475-491."""
+    from lidar_ai_solution_b200 import infer
+    a = infer.parse_args(["--onnx", "m.onnx", "--feature", "f", "--indice", "i",
+                          "--grid_size", "41,1440,1440"])
+    assert a.fp16 and not a.int8 and not a.cudagraph and not a.dds and not a.profiling
+    assert a.fixed_points == 10000 and not a.search_best_perf and not a.stress
+    a = infer.parse_args(["--synthetic", "centerpoint", "--int8", "--cudagraph=true", "--dds",
+                          "--blackwell", "--sortmask=false", "--fixed_points", "4096"])
+    assert a.int8 and a.cudagraph and a.dds and a.blackwell and not a.sortmask
+    assert a.fixed_points == 4096
