@@ -388,7 +388,7 @@ def run_gpu(args, rank, world, local_rank):
         achieved = conv_bytes / (conv_ms / 1000.0) / 1e9 if conv_ms > 0 else 0.0
         line["roofline"] = {
             "bound": "hbm",
-            "kernel": "conv_umma_m_kernel + conv_umma_n_kernel (all %d convolution launches of a frame)" % n_conv,
+            "kernel": "conv_umma_kernel (all %d convolution launches of a frame)" % n_conv,
             "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
             "peak_source": "measured" if "hbm_gbs" in peaks else "fallback",
             "traffic": CONV_DRAM_PER_ALGORITHMIC_BYTE * conv_bytes,

@@ -1,14 +1,12 @@
-// Tensor-core convolution: what the two kernel variants share on the host side (the
-// supported shapes, the pre-swizzled weight image both read) and the choice between them.
+// Tensor-core convolution, host side: the supported shapes, the pre-swizzled weight
+// image the kernel streams, argument checks and the launch.
 #include "umma_common.cuh"
 
 namespace spconvb {
 
 using namespace umma_detail;
 
-int conv_umma_m_launch(const UmmaArgs& a, bool int8, int rb, int cout, uint32_t launch_rows,
-                       cudaStream_t st);
-int conv_umma_n_launch(const UmmaArgs& a, bool int8, int rb, int cout, uint32_t launch_rows,
+int conv_umma_kernel_launch(const UmmaArgs& a, bool int8, int rb, int cout, uint32_t launch_rows,
                        cudaStream_t st);
 
 bool conv_umma_supported(int compute, int cin, int cout) {
@@ -68,12 +66,7 @@ int conv_umma_launch(const spconvb_conv_params& p, const void* in, const int32_t
   a.kvol = p.kvol;
   a.ep = make_epilogue(p);
   const int rb = row_bytes(p.compute, p.cin);
-  // Wide outputs fill the 128 accumulator lanes when the channels sit on the M side and
-  // 256 voxel rows on the N side; for narrow outputs most lanes would idle and the
-  // epilogue, which works per lane, would dominate: those keep the rows on the M side.
-  if (p.cout >= 64)
-    return conv_umma_n_launch(a, p.compute == SPCONVB_I8, rb, p.cout, launch_rows, st);
-  return conv_umma_m_launch(a, p.compute == SPCONVB_I8, rb, p.cout, launch_rows, st);
+  return conv_umma_kernel_launch(a, p.compute == SPCONVB_I8, rb, p.cout, launch_rows, st);
 }
 
 }  // namespace spconvb

@@ -1,5 +1,5 @@
 // Sparse convolution as an implicit GEMM on the sm_100a tensor cores, voxel rows on
-// the N side of the MMA (the variant used for wide outputs, Cout >= 64).
+// the N side of the MMA.
 //
 //   out[o, :] = epilogue( sum_k  W[:, k, :] . in[map[k][o], :] )
 //
@@ -8,14 +8,16 @@
 // feature rows of o's neighbours (zeros where a neighbour is absent).  A
 // tcgen05.mma with 128 accumulator lanes takes the same time whether it is 16
 // or 256 columns wide, so the voxel rows are put on the wide side: the weights
-// are the M operand (128 lanes = output channels, the lanes beyond Cout compute
-// on whatever follows the weights in shared memory and are never read), a tile
-// of 256 voxel rows is the N operand, and the accumulator in TMEM is the
-// transposed output tile  D[channel][row].  The kernel is persistent (one CTA
-// per SM) and warp-specialised:
+// are the M operand (128 accumulator lanes = output channels), a tile of 256
+// voxel rows is the N operand, and the accumulator in TMEM is the transposed
+// output tile  D[channel][row].  With fewer than 128 output channels the weight
+// chunk is copied 128 / Cout times into the M operand, so that every lane
+// quadrant holds all channels and the epilogue warps of different quadrants can
+// share the rows of the tile between them instead of idling.  The kernel is
+// persistent (one CTA per SM) and warp-specialised:
 //
 //   warps 0-7   epilogue: warp w reads lanes 32*(w%4).. (its channels) and
-//               columns 128*(w/4).. (its rows) of the accumulator with
+//               Cout columns (its share of the tile's rows) of the accumulator with
 //               tcgen05.ld, applies dequant + bias + activation (+ residual
 //               add) + requant with per-lane scale and bias, transposes 4x4
 //               blocks inside lane quads with two shuffles, and stores 4 (int8)
@@ -55,10 +57,10 @@ constexpr int kMmaM = 128;      // accumulator lanes: output channels, padded
 template <int COUT>
 struct Ring {
   // as deep as shared memory allows next to the index staging area
-  static constexpr int kStages = COUT <= 32 ? 5 : 4;
+  static constexpr int kStages = 4;
   // A producer signals a stage "full" kLag chunks after issuing its copies; the
   // other kStages - kLag stages are slack for the round trip through the MMA.
-  static constexpr int kLag = COUT <= 32 ? 2 : 1;
+  static constexpr int kLag = 1;
 };
 constexpr int kRowsBytes = kTileRows * kChunk;  // gathered rows of one stage
 constexpr int kEpiWarps = 8;
@@ -123,23 +125,25 @@ __device__ __forceinline__ void quad_transpose_h16(uint32_t& w0, uint32_t& w1, u
 
 template <int COUT>
 constexpr size_t umma_smem_bytes() {
-  return 1024 + (size_t)Ring<COUT>::kStages * (kRowsBytes + COUT * kChunk) +
+  return 1024 + (size_t)Ring<COUT>::kStages * (kRowsBytes + kMmaM * kChunk) +
          (size_t)kMaxTaps * kTileRows * sizeof(int32_t) + 256;
 }
 
 // ------------------------------------------------------------------- kernel
 template <bool INT8, int RB, int COUT>
-__global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_n_kernel(const UmmaArgs a) {
-  constexpr int kWBytes = COUT * kChunk;
+__global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArgs a) {
+  constexpr int kWBytes = kMmaM * kChunk;      // weight stage: kReplicas copies of the chunk
+  constexpr int kWChunk = COUT * kChunk;       // one copy, as packed in global memory
+  constexpr int kReplicas = kMmaM / COUT;
   constexpr int kStages = Ring<COUT>::kStages;
   constexpr int kLag = Ring<COUT>::kLag;
   constexpr int OPC = RB <= kChunk ? kChunk / RB : 1;   // taps per chunk
   constexpr int SPO = RB <= kChunk ? RB / 16 : 8;       // 16-byte segments per tap per chunk
   constexpr int CPT = RB <= kChunk ? 1 : RB / kChunk;   // chunks per tap
 
-  // Shared memory: the weight stages come first, so that the accumulator lanes
-  // beyond Cout read the (valid) bytes behind them; then the gathered-row stages,
-  // the neighbour indices of the current tile, the barriers.
+  // Shared memory: the weight stages (128 rows each: the replicated chunk), the
+  // gathered-row stages, the producers' neighbour indices of the current tile, the
+  // barriers.
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
@@ -249,8 +253,10 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_n_kernel(const UmmaA
         }
         if (r == 0) {
           mbar_expect_tx(bar_full + 8 * s, kWBytes);
-          bulk_g2s(smem_u32(sW + s * kWBytes), a.wpk + (size_t)j * kWBytes, kWBytes,
-                   bar_full + 8 * s);
+#pragma unroll
+          for (int c = 0; c < kReplicas; ++c)
+            bulk_g2s(smem_u32(sW + s * kWBytes + c * kWChunk), a.wpk + (size_t)j * kWChunk,
+                     kWChunk, bar_full + 8 * s);
         }
         const int k = (RB <= kChunk) ? j * OPC + (int)seg_tap : j / CPT;
         const uint32_t byte = seg_byte + (RB > kChunk ? (uint32_t)(j % CPT) * kChunk : 0u);
@@ -335,15 +341,22 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_n_kernel(const UmmaA
     // as one saturating round-to-nearest-even convert, and the layer-wide switches
     // hoisted out of the element loops.
     const Epilogue ep = a.ep;
+    // The weights are replicated kReplicas times along the accumulator lanes, so every
+    // lane holds a valid channel; replica r owns the tile's rows [r, r + 1) * 2 * COUT, and
+    // the two warps of a lane quadrant split those rows again.  Each warp thus works on
+    // COUT rows of the tile: COUT / 16 groups of 16.
     const uint32_t q = (uint32_t)warp & 3u;        // TMEM lane quadrant of this warp
-    const uint32_t half = (uint32_t)warp >> 2;     // column half of this warp
-    const bool warp_active = 32u * q < (uint32_t)COUT;
-    const uint32_t ch = 32u * q + lane;            // this lane's channel in the accumulator
-    const uint32_t chq = 32u * q + (lane & ~3u);   // first of the 4 channels this lane stores
+    const uint32_t half = (uint32_t)warp >> 2;
+    const uint32_t acc_lane = 32u * q + lane;
+    const uint32_t ch = acc_lane % COUT;           // this lane's channel
+    const uint32_t chq = ch & ~3u;                 // first of the 4 channels this lane stores
     const uint32_t j4 = lane & 3u;                 // row within a group of 4 this lane stores
-    const bool chq_ok = chq < (uint32_t)COUT;
-    const float sc = (INT8 && ch < (uint32_t)COUT && a.scale) ? __ldg(a.scale + ch) : 1.f;
-    const float bi = (ch < (uint32_t)COUT && a.bias) ? __ldg(a.bias + ch) : 0.f;
+    // first row (of the tile) of this lane, and of lane 0 of the warp: they differ only for
+    // COUT = 16, where the two halves of a warp belong to different replicas
+    const uint32_t col_lane = (acc_lane / COUT) * (2u * COUT) + half * COUT;
+    const uint32_t col_warp = ((32u * q) / COUT) * (2u * COUT) + half * COUT;
+    const float sc = (INT8 && a.scale) ? __ldg(a.scale + ch) : 1.f;
+    const float bi = a.bias ? __ldg(a.bias + ch) : 0.f;
     const float lo = ep.act == SPCONVB_ACT_RELU ? 0.f : -INFINITY;
     const float lo2 = ep.res_relu ? 0.f : -INFINITY;
     const bool res_i8 = ep.res_kind == SPCONVB_I8;
@@ -356,7 +369,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_n_kernel(const UmmaA
       for (int t = 0; t < 4; ++t) {
         const uint32_t row = res_i8 ? row0 + 4u * j4 + t : row0 + 4u * t + j4;
         rq[t] = make_uint2(0u, 0u);
-        if (row < n_out && chq_ok) {
+        if (row < n_out) {
           const uint8_t* p = a.res + ((size_t)row * COUT + chq) * res_b;
           if (res_i8) rq[t].x = __ldg((const uint32_t*)p);
           else rq[t] = __ldg((const uint2*)p);
@@ -366,13 +379,14 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_n_kernel(const UmmaA
     uint32_t tl = 0;
     for (uint32_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++tl) {
       const uint32_t buf = tl & 1u;
-      const uint32_t trow0 = tile * kTileRows + half * (kTileRows / 2);
+      const uint32_t trow0 = tile * kTileRows + col_lane;
       // the first residual rows are fetched before the accumulator is waited for;
       // after that the loads run two groups of 16 rows ahead of the arithmetic
+      constexpr int kGroups = COUT / 16;
       uint2 rq0[4], rq1[4];
-      if (warp_active && ep.has_res) {
+      if (ep.has_res) {
         load_res(trow0, rq0);
-        load_res(trow0 + 16, rq1);
+        if (kGroups > 1) load_res(trow0 + 16, rq1);
       }
       uint32_t ok = 1u;
       if (lane == 0)
@@ -380,24 +394,19 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_n_kernel(const UmmaA
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       tc_fence_after();
-      if (!warp_active) {
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
-        continue;
-      }
-      const uint32_t taddr = tmem_base + ((32u * q) << 16) + buf * kTileRows +
-                             half * (kTileRows / 2);
-      constexpr int kGroups = kTileRows / 2 / 16;
-      uint32_t vn[16];
-      tmem_ld16(taddr, vn);  // the accumulator load of group g + 1 overlaps the work on g
+      const uint32_t taddr = tmem_base + ((32u * q) << 16) + buf * kTileRows + col_warp;
+      // the accumulator load of group g + 1 overlaps the work on g; with COUT = 16 the upper
+      // half of the warp takes its columns from a second load, 2 * COUT columns further on
+      uint32_t vn[16], vm[16];
+      tmem_ld16(taddr, vn);
+      if (COUT == 16) tmem_ld16(taddr + 2u * COUT, vm);
 #pragma unroll
       for (int g = 0; g < kGroups; ++g) {
         const uint32_t row0 = trow0 + 16u * g;
         uint32_t v[16];
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 16; ++i) v[i] = vn[i];
+        for (int i = 0; i < 16; ++i) v[i] = (COUT == 16 && lane >= 16u) ? vm[i] : vn[i];
         if (g + 1 < kGroups) {
           tmem_ld16(taddr + 16u * (g + 1), vn);
         } else {
@@ -471,7 +480,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_n_kernel(const UmmaA
 #pragma unroll
           for (int t = 0; t < 4; ++t) {
             const uint32_t row = row0 + 4u * j4 + t;
-            if (row < n_out && chq_ok) *(uint32_t*)(a.out + (size_t)row * COUT + chq) = w[t];
+            if (row < n_out) *(uint32_t*)(a.out + (size_t)row * COUT + chq) = w[t];
           }
         } else {
 #pragma unroll
@@ -481,7 +490,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_n_kernel(const UmmaA
             uint32_t w0 = *(uint32_t*)&h0, w1 = *(uint32_t*)&h1;
             quad_transpose_h16(w0, w1, lane);
             const uint32_t row = row0 + 4u * t + j4;
-            if (row < n_out && chq_ok)
+            if (row < n_out)
               *(uint2*)(a.out + ((size_t)row * COUT + chq) * out_b) = make_uint2(w0, w1);
           }
         }
@@ -514,14 +523,14 @@ int launch_one(const UmmaArgs& args, uint32_t launch_rows, cudaStream_t st) {
   SPCONVB_CUDA_TRY(cudaGetDevice(&dev));
   constexpr size_t smem = umma_smem_bytes<COUT>();
   if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-    SPCONVB_CUDA_TRY(cudaFuncSetAttribute(conv_umma_n_kernel<INT8, RB, COUT>,
+    SPCONVB_CUDA_TRY(cudaFuncSetAttribute(conv_umma_kernel<INT8, RB, COUT>,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           (int)smem));
     if (dev >= 0 && dev < 64) attr_done[dev] = true;
   }
   uint32_t tiles = (launch_rows + kTileRows - 1) / kTileRows;
   int grid = (int)(tiles < (uint32_t)kSmCount ? (tiles ? tiles : 1u) : (uint32_t)kSmCount);
-  conv_umma_n_kernel<INT8, RB, COUT><<<grid, kCtaThreads, smem, st>>>(args);
+  conv_umma_kernel<INT8, RB, COUT><<<grid, kCtaThreads, smem, st>>>(args);
   SPCONVB_LAUNCH_CHECK();
   return SPCONVB_OK;
 }
@@ -551,7 +560,7 @@ int launch_rb(int rb, int cout, const UmmaArgs& args, uint32_t launch_rows, cuda
 
 }  // namespace
 
-int conv_umma_n_launch(const UmmaArgs& a, bool int8, int rb, int cout, uint32_t launch_rows,
+int conv_umma_kernel_launch(const UmmaArgs& a, bool int8, int rb, int cout, uint32_t launch_rows,
                        cudaStream_t st) {
   return int8 ? launch_rb<true>(rb, cout, a, launch_rows, st)
               : launch_rb<false>(rb, cout, a, launch_rows, st);

@@ -1,8 +1,7 @@
-// Pieces shared by the two tensor-core convolution kernels (conv_umma_m.cu keeps the
-// voxel rows on the M side of the MMA, conv_umma_n.cu on the N side): the kernel
-// arguments, thin wrappers over the PTX they use (mbarrier, cp.async, bulk copy,
-// tcgen05 alloc/mma/commit/ld), the shared-memory operand descriptor and the
-// bounded wait.
+// What the tensor-core convolution kernel (conv_umma_kernel.cu) and its host side
+// (conv_umma.cu) share: the kernel arguments, thin wrappers over the PTX the kernel
+// uses (mbarrier, cp.async, bulk copy, tcgen05 alloc/mma/commit/ld), the
+// shared-memory operand descriptor and the bounded wait.
 #pragma once
 #include "common.cuh"
 

@@ -208,8 +208,8 @@ def test_conv_int8_ragged_row_counts(n):
 @pytest.mark.parametrize("n", [1, 3, 255, 256, 257, 511, 513])
 @pytest.mark.parametrize("out_kind", ["i8", "f16"])
 def test_conv_int8_ragged_row_counts_wide_outputs(n, out_kind):
-    """Cout >= 64 runs the kernel variant with 256-row tiles: partial tiles, partial
-    groups of 4 rows in the transposing epilogue, single-row inputs."""
+    """Tiles are 256 rows and the epilogue stores groups of 4 rows per lane quad: partial
+    tiles, partial groups, single-row inputs, with 2 weight replicas on the lanes."""
     kind = orc.KIND_I8 if out_kind == "i8" else orc.KIND_F16
     got, ref = _int8_layer(n, 32, 64, seed=100 + n, simt=False, out_kind=kind, grid=(7, 11, 13))
     assert np.array_equal(got.view(np.uint8), ref.view(np.uint8))
@@ -271,9 +271,9 @@ def test_conv_fp16_cuda_core_bit_exact_and_first_layer_padding():
 @pytest.mark.parametrize("c,n", [(16, 5000), (32, 5001), (64, 5000), (64, 4999), (128, 2050)])
 @pytest.mark.parametrize("res_kind", ["i8", "f16"])
 def test_conv_int8_fused_residual_all_widths(c, n, res_kind):
-    """Fused conv + Add&ReLU == oracle conv (stored int8) followed by oracle add, for both
-    kernel variants (Cout < 64 and >= 64), int8 and fp16 residual operands, row counts
-    that leave partial tiles."""
+    """Fused conv + Add&ReLU == oracle conv (stored int8) followed by oracle add, for every
+    output width (8, 4, 2 or 1 copies of the weights on the accumulator lanes), int8 and
+    fp16 residual operands, row counts that leave partial tiles."""
     ops = _ops()
     grid = (41, 180, 180)
     pb = int8_problem(n, c, c, grid, seed=40 + c)
