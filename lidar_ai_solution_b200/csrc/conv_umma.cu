@@ -64,6 +64,20 @@ int conv_umma_launch(const spconvb_conv_params& p, const void* in, const int32_t
   a.out = (uint8_t*)out;
   a.status = status;
   a.kvol = p.kvol;
+  // Copies of the weights along the accumulator lanes, and residency.  Every copy lets
+  // more epilogue warps share a tile, but a streamed stage always moves 128 weight rows,
+  // as much L2 traffic as the gathered rows cost.  So: the most copies with which all
+  // chunks of the layer still fit in the 64 KB the weight stages occupy, loaded once;
+  // if not even one copy fits, stream with full replication.
+  {
+    const int rbytes = row_bytes(p.compute, p.cin);
+    const size_t nchunk = ((size_t)p.kvol * rbytes + kChunk - 1) / kChunk;
+    const int full = 128 / p.cout;
+    int rep = full;
+    while (rep >= 1 && nchunk * (size_t)rep * p.cout * kChunk > 65536) rep /= 2;
+    a.w_resident = rep >= 1;
+    a.w_rep = rep >= 1 ? rep : full;
+  }
   a.ep = make_epilogue(p);
   const int rb = row_bytes(p.compute, p.cin);
   return conv_umma_kernel_launch(a, p.compute == SPCONVB_I8, rb, p.cout, launch_rows, st);

@@ -11,10 +11,14 @@
 // are the M operand (128 accumulator lanes = output channels), a tile of 256
 // voxel rows is the N operand, and the accumulator in TMEM is the transposed
 // output tile  D[channel][row].  With fewer than 128 output channels the weight
-// chunk is copied 128 / Cout times into the M operand, so that every lane
-// quadrant holds all channels and the epilogue warps of different quadrants can
-// share the rows of the tile between them instead of idling.  The kernel is
-// persistent (one CTA per SM) and warp-specialised:
+// chunk is copied several times into the M operand, so that more lane quadrants
+// hold all channels and the epilogue warps of different quadrants can share the
+// rows of the tile between them instead of idling.  When all chunks of the layer
+// (times the copies) fit in 64 KB they are loaded once and stay in shared memory;
+// otherwise a chunk is streamed with every stage.  Streaming costs as much L2
+// traffic as the gathers themselves (128 weight rows per 256 gathered rows), so
+// the host side trades copies for residency.  The kernel is persistent (one CTA
+// per SM) and warp-specialised:
 //
 //   warps 0-7   epilogue: warp w reads lanes 32*(w%4).. (its channels) and
 //               Cout columns (its share of the tile's rows) of the accumulator with
@@ -37,7 +41,7 @@
 //
 // K is walked in chunks of 128 bytes (one swizzle atom per row): a chunk is 8
 // taps of a 16-byte row, ..., 1 tap of a 128-byte row, or half a 256-byte row.
-// Stages cycle through a 4- or 5-deep ring guarded by mbarriers; the accumulator
+// Stages cycle through a 4-deep ring guarded by mbarriers; the accumulator
 // is double-buffered in TMEM (2 x 256 columns) so the epilogue of tile t
 // overlaps the MMAs of tile t+1.
 //
@@ -52,7 +56,7 @@ using namespace umma_detail;
 
 namespace {
 
-constexpr int kTileRows = 256;  // voxel rows per tile: the N of the MMA
+constexpr int kTileRows = 256;  // most voxel rows per tile: the largest N of the MMA
 constexpr int kMmaM = 128;      // accumulator lanes: output channels, padded
 template <int COUT>
 struct Ring {
@@ -76,7 +80,7 @@ constexpr uint32_t kTmemCols = 2 * kTileRows;
 template <bool INT8>
 __device__ __forceinline__ constexpr uint32_t make_idesc() {
   return (INT8 ? ((2u << 4) | (1u << 7) | (1u << 10)) : (1u << 4)) |
-         ((uint32_t)(kTileRows >> 3) << 17) | ((uint32_t)(kMmaM >> 4) << 24);
+         ((uint32_t)(kMmaM >> 4) << 24);  // N is added per launch: (tile rows >> 3) << 17
 }
 
 // Transposes inside a quad of lanes (lane = 4g + j): they turn "my channel for a
@@ -132,9 +136,8 @@ constexpr size_t umma_smem_bytes() {
 // ------------------------------------------------------------------- kernel
 template <bool INT8, int RB, int COUT>
 __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArgs a) {
-  constexpr int kWBytes = kMmaM * kChunk;      // weight stage: kReplicas copies of the chunk
-  constexpr int kWChunk = COUT * kChunk;       // one copy, as packed in global memory
-  constexpr int kReplicas = kMmaM / COUT;
+  constexpr int kWBytes = kMmaM * kChunk;      // weight stage when streaming: 128 rows
+  constexpr int kWChunk = COUT * kChunk;       // one copy of a chunk, as packed in global memory
   constexpr int kStages = Ring<COUT>::kStages;
   constexpr int kLag = Ring<COUT>::kLag;
   constexpr int OPC = RB <= kChunk ? kChunk / RB : 1;   // taps per chunk
@@ -151,13 +154,14 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
   uint8_t* sR = sW + kStages * kWBytes;
   int32_t* sIdx = (int32_t*)(sR + kStages * kRowsBytes);  // [kMaxTaps][kTileRows]
   uint64_t* bars = (uint64_t*)(sIdx + kMaxTaps * kTileRows);
-  uint32_t* tmem_holder = (uint32_t*)(bars + 2 * kStages + 4);
+  uint32_t* tmem_holder = (uint32_t*)(bars + 2 * kStages + 5);
   volatile uint32_t* abort_flag = tmem_holder + 1;
 
   const uint32_t bar_full = smem_u32(bars);
   const uint32_t bar_empty = bar_full + 8 * kStages;
   const uint32_t bar_tfull = bar_empty + 8 * kStages;
   const uint32_t bar_tempty = bar_tfull + 16;
+  const uint32_t bar_w = bar_tempty + 16;  // resident weights have landed
 
   const int warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31;
@@ -171,6 +175,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
       mbar_init(bar_tfull + 8 * b, 1);
       mbar_init(bar_tempty + 8 * b, kEpiWarps);
     }
+    mbar_init(bar_w, 1);
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async();
@@ -188,10 +193,21 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
   const uint32_t tmem_base = *tmem_holder;
 
   const uint32_t n_out = min(*a.n_out_ptr, a.cap);
-  const uint32_t ntiles = (n_out + kTileRows - 1) / kTileRows;
+  // Tile height: the rows are dealt out in rounds over the CTAs, so a fixed 256-row tile
+  // can leave most CTAs idle in the last round (227 tiles on 148 CTAs run as long as 296).
+  // The height is instead the smallest multiple of 32 with which every CTA gets the same
+  // number of tiles: per-CTA rows / rounds, rounded up.
+  const uint32_t per_cta = (n_out + gridDim.x - 1) / gridDim.x;
+  const uint32_t rounds = max(1u, (per_cta + kTileRows - 1) / kTileRows);
+  const uint32_t tile_rows =
+      min((uint32_t)kTileRows, max(32u, ((per_cta + rounds - 1) / rounds + 31u) & ~31u));
+  const uint32_t ntiles = (n_out + tile_rows - 1) / tile_rows;
   const int kbytes = a.kvol * RB;
   const int nchunk = (kbytes + kChunk - 1) / kChunk;
   const int last_ksteps = ((kbytes - (nchunk - 1) * kChunk) + 31) / 32;
+  const uint32_t w_rep = (uint32_t)a.w_rep;
+  const bool w_resident = a.w_resident != 0;
+  const uint32_t w_chunk_smem = w_rep * kWChunk;  // bytes of one chunk with its copies
 
   if (warp >= kProdWarp0) {
     // ------------------------------------------------------------ producers
@@ -220,8 +236,8 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
     // needs for a tap are two 16-byte loads.
     int32_t* widx = sIdx + pw * (kMaxTaps * 32);
     auto fetch_indices = [&](uint32_t tile, int32_t (&v)[kMaxTaps]) {
-      const uint32_t row = tile * kTileRows + pw * 32u + lane;
-      const bool valid = tile < ntiles && row < n_out;
+      const uint32_t row = tile * tile_rows + pw * 32u + lane;
+      const bool valid = tile < ntiles && row < n_out && pw * 32u < tile_rows;
       const int32_t* src = a.map + row;
 #pragma unroll
       for (int k = 0; k < kMaxTaps; ++k)
@@ -236,8 +252,16 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
     };
     uint32_t it = 0;
     bool alive = true;
+    const bool has_rows = pw * 32u < tile_rows;  // else this warp only keeps the barriers going
     int32_t nxt[kMaxTaps];
     fetch_indices(blockIdx.x, nxt);
+    if (r == 0 && w_resident && blockIdx.x < ntiles) {
+      mbar_expect_tx(bar_w, (uint32_t)nchunk * w_chunk_smem);
+      for (int j = 0; j < nchunk; ++j)
+        for (uint32_t c = 0; c < w_rep; ++c)
+          bulk_g2s(smem_u32(sW + j * w_chunk_smem + c * kWChunk), a.wpk + (size_t)j * kWChunk,
+                   kWChunk, bar_w);
+    }
     for (uint32_t tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x) {
       __syncwarp();  // the warp's reads of the previous tile's indices are done
 #pragma unroll
@@ -252,28 +276,33 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
           break;
         }
         if (r == 0) {
-          mbar_expect_tx(bar_full + 8 * s, kWBytes);
-#pragma unroll
-          for (int c = 0; c < kReplicas; ++c)
-            bulk_g2s(smem_u32(sW + s * kWBytes + c * kWChunk), a.wpk + (size_t)j * kWChunk,
-                     kWChunk, bar_full + 8 * s);
+          if (w_resident) {
+            mbar_arrive(bar_full + 8 * s);
+          } else {
+            mbar_expect_tx(bar_full + 8 * s, w_chunk_smem);
+            for (uint32_t c = 0; c < w_rep; ++c)
+              bulk_g2s(smem_u32(sW + s * kWBytes + c * kWChunk), a.wpk + (size_t)j * kWChunk,
+                       kWChunk, bar_full + 8 * s);
+          }
         }
         const int k = (RB <= kChunk) ? j * OPC + (int)seg_tap : j / CPT;
         const uint32_t byte = seg_byte + (RB > kChunk ? (uint32_t)(j % CPT) * kChunk : 0u);
         // taps beyond the staged ones (K padding of the last chunk) gather nothing;
         // staged taps beyond kvol hold -1
         const bool staged = k < kMaxTaps;
-        const int4* idx_k = (const int4*)(widx + (staged ? k : 0) * 32 + slot * 8u);
-        const uint32_t stage_addr = smem_u32(sR + s * kRowsBytes);
-        const int4 ia = idx_k[0], ib = idx_k[1];
-        int32_t src_row[8] = {ia.x, ia.y, ia.z, ia.w, ib.x, ib.y, ib.z, ib.w};
+        if (has_rows) {
+          const int4* idx_k = (const int4*)(widx + (staged ? k : 0) * 32 + slot * 8u);
+          const uint32_t stage_addr = smem_u32(sR + s * kRowsBytes);
+          const int4 ia = idx_k[0], ib = idx_k[1];
+          int32_t src_row[8] = {ia.x, ia.y, ia.z, ia.w, ib.x, ib.y, ib.z, ib.w};
 #pragma unroll
-        for (int i = 0; i < 8; ++i) src_row[i] = staged ? src_row[i] : -1;
+          for (int i = 0; i < 8; ++i) src_row[i] = staged ? src_row[i] : -1;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int32_t sr = src_row[i];
-          cp_async16(stage_addr + ((i & 1) ? dst_odd : dst_even) + (uint32_t)(i >> 1) * 1024u,
-                     a.in + (size_t)(sr < 0 ? 0 : sr) * RB + byte, sr < 0 ? 0u : 16u);
+          for (int i = 0; i < 8; ++i) {
+            const int32_t sr = src_row[i];
+            cp_async16(stage_addr + ((i & 1) ? dst_odd : dst_even) + (uint32_t)(i >> 1) * 1024u,
+                       a.in + (size_t)(sr < 0 ? 0 : sr) * RB + byte, sr < 0 ? 0u : 16u);
+          }
         }
         cp_async_commit();
         if (it >= (uint32_t)kLag) {
@@ -299,12 +328,14 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
       // second-to-last and the last MMA of a chunk, or is short: the next stage's
       // barrier is probed while the pipe is busy, so that the first MMA of the next
       // chunk can follow the last one of this chunk without a bubble.
-      constexpr uint32_t idesc = make_idesc<INT8>();
+      const uint32_t idesc = make_idesc<INT8>() | ((tile_rows >> 3) << 17);
       const uint64_t wdesc0 = make_smem_desc(smem_u32(sW));  // M operand: weights
       const uint64_t rdesc0 = make_smem_desc(smem_u32(sR));  // N operand: gathered rows
       uint32_t s = 0, ph = 0, tl = 0;
       bool ready = false;  // full[s] already seen complete by a probe
       bool alive = true;
+      if (w_resident && blockIdx.x < ntiles)
+        alive = mbar_wait(bar_w, 0u, abort_flag, a.status, 6u);
       for (uint32_t tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x, ++tl) {
         const uint32_t buf = tl & 1u;
         if (!mbar_wait(bar_tempty + 8 * buf, ((tl >> 1) & 1u) ^ 1u, abort_flag, a.status, 2u))
@@ -316,7 +347,8 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
             break;
           }
           tc_fence_after();
-          const uint64_t wd = wdesc0 + (uint64_t)(s * (uint32_t)(kWBytes >> 4));
+          const uint64_t wd = wdesc0 + (uint64_t)(w_resident ? (uint32_t)j * (w_chunk_smem >> 4)
+                                                             : s * (uint32_t)(kWBytes >> 4));
           const uint64_t rd = rdesc0 + (uint64_t)(s * (uint32_t)(kRowsBytes >> 4));
           const int nk = (j == nchunk - 1) ? last_ksteps : kChunk / 32;
           for (int ks = 0; ks + 1 < nk; ++ks)
@@ -341,20 +373,23 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
     // as one saturating round-to-nearest-even convert, and the layer-wide switches
     // hoisted out of the element loops.
     const Epilogue ep = a.ep;
-    // The weights are replicated kReplicas times along the accumulator lanes, so every
-    // lane holds a valid channel; replica r owns the tile's rows [r, r + 1) * 2 * COUT, and
-    // the two warps of a lane quadrant split those rows again.  Each warp thus works on
-    // COUT rows of the tile: COUT / 16 groups of 16.
+    // The weights are copied w_rep times along the accumulator lanes: lanes below
+    // w_rep * COUT hold a valid channel.  Copy r owns the tile's rows [r, r + 1) * 256 /
+    // w_rep, and the two warps of a lane quadrant split those rows again, so a warp works
+    // on 128 / w_rep rows of the tile: 8 / w_rep groups of 16.
     const uint32_t q = (uint32_t)warp & 3u;        // TMEM lane quadrant of this warp
     const uint32_t half = (uint32_t)warp >> 2;
     const uint32_t acc_lane = 32u * q + lane;
     const uint32_t ch = acc_lane % COUT;           // this lane's channel
     const uint32_t chq = ch & ~3u;                 // first of the 4 channels this lane stores
     const uint32_t j4 = lane & 3u;                 // row within a group of 4 this lane stores
+    const uint32_t cols_rep = (uint32_t)kTileRows / w_rep, cols_warp = cols_rep / 2u;
+    const bool lane_active = acc_lane / COUT < w_rep;
+    const bool warp_active = (32u * q) / COUT < w_rep;
     // first row (of the tile) of this lane, and of lane 0 of the warp: they differ only for
-    // COUT = 16, where the two halves of a warp belong to different replicas
-    const uint32_t col_lane = (acc_lane / COUT) * (2u * COUT) + half * COUT;
-    const uint32_t col_warp = ((32u * q) / COUT) * (2u * COUT) + half * COUT;
+    // COUT = 16, where the two halves of a warp belong to different copies
+    const uint32_t col_lane = (acc_lane / COUT) * cols_rep + half * cols_warp;
+    const uint32_t col_warp = ((32u * q) / COUT) * cols_rep + half * cols_warp;
     const float sc = (INT8 && a.scale) ? __ldg(a.scale + ch) : 1.f;
     const float bi = a.bias ? __ldg(a.bias + ch) : 0.f;
     const float lo = ep.act == SPCONVB_ACT_RELU ? 0.f : -INFINITY;
@@ -364,12 +399,12 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
     const uint32_t res_b = res_i8 ? 1u : 2u;
     // residual words of 16 rows: lane (g, j) loads channels 4g..4g+3 of rows 4j + t
     // (int8, a word each) or of rows 4t + j (fp16, two words each), t = 0..3
-    auto load_res = [&](uint32_t row0, uint2 (&rq)[4]) {
+    auto load_res = [&](uint32_t row0, bool in_tile, uint2 (&rq)[4]) {
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
         const uint32_t row = res_i8 ? row0 + 4u * j4 + t : row0 + 4u * t + j4;
         rq[t] = make_uint2(0u, 0u);
-        if (row < n_out) {
+        if (in_tile && row < n_out) {
           const uint8_t* p = a.res + ((size_t)row * COUT + chq) * res_b;
           if (res_i8) rq[t].x = __ldg((const uint32_t*)p);
           else rq[t] = __ldg((const uint2*)p);
@@ -379,37 +414,47 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
     uint32_t tl = 0;
     for (uint32_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++tl) {
       const uint32_t buf = tl & 1u;
-      const uint32_t trow0 = tile * kTileRows + col_lane;
+      const uint32_t trow0 = tile * tile_rows + col_lane;
       // the first residual rows are fetched before the accumulator is waited for;
-      // after that the loads run two groups of 16 rows ahead of the arithmetic
-      constexpr int kGroups = COUT / 16;
-      uint2 rq0[4], rq1[4];
-      if (ep.has_res) {
-        load_res(trow0, rq0);
-        if (kGroups > 1) load_res(trow0 + 16, rq1);
-      }
+      // after that the loads run one group of 16 rows ahead of the arithmetic.  A group
+      // lies inside the tile or not as a whole (the tile height is a multiple of 32);
+      // rows past it belong to the next tile.
+      uint2 rq[4];
+      if (ep.has_res) load_res(trow0, lane_active && col_lane < tile_rows, rq);
       uint32_t ok = 1u;
       if (lane == 0)
         ok = mbar_wait(bar_tfull + 8 * buf, (tl >> 1) & 1u, abort_flag, a.status, 4u) ? 1u : 0u;
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       tc_fence_after();
+      // groups of this warp that lie inside the tile (by its lower-numbered rows)
+      const uint32_t ng = (!warp_active || col_warp >= tile_rows)
+                              ? 0u
+                              : min(cols_warp / 16u, (tile_rows - col_warp + 15u) / 16u);
       const uint32_t taddr = tmem_base + ((32u * q) << 16) + buf * kTileRows + col_warp;
-      // the accumulator load of group g + 1 overlaps the work on g; with COUT = 16 the upper
-      // half of the warp takes its columns from a second load, 2 * COUT columns further on
-      uint32_t vn[16], vm[16];
-      tmem_ld16(taddr, vn);
-      if (COUT == 16) tmem_ld16(taddr + 2u * COUT, vm);
-#pragma unroll
-      for (int g = 0; g < kGroups; ++g) {
+      if (ng == 0u) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+      }
+#pragma unroll 1
+      for (uint32_t g = 0; g < ng; ++g) {
         const uint32_t row0 = trow0 + 16u * g;
+        const bool in_tile = lane_active && col_lane + 16u * g < tile_rows;
         uint32_t v[16];
-        tmem_ld_wait();
+        tmem_ld16(taddr + 16u * g, v);
+        if (COUT == 16 && w_rep > 1u) {
+          // the upper half of the warp belongs to the next copy: its rows are one copy's
+          // worth of columns further on
+          uint32_t vm[16];
+          tmem_ld16(taddr + cols_rep + 16u * g, vm);
+          tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 16; ++i) v[i] = (COUT == 16 && lane >= 16u) ? vm[i] : vn[i];
-        if (g + 1 < kGroups) {
-          tmem_ld16(taddr + 16u * (g + 1), vn);
+          for (int i = 0; i < 16; ++i) v[i] = lane >= 16u ? vm[i] : v[i];
         } else {
+          tmem_ld_wait();
+        }
+        if (g + 1u == ng) {
           // every accumulator element of this warp is in registers: release the buffer
           tc_fence_before();
           __syncwarp();
@@ -418,11 +463,9 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
         uint2 rcur[4];
         if (ep.has_res) {
 #pragma unroll
-          for (int t = 0; t < 4; ++t) {
-            rcur[t] = rq0[t];
-            rq0[t] = rq1[t];
-          }
-          if (g + 2 < kGroups) load_res(row0 + 32, rq1);
+          for (int t = 0; t < 4; ++t) rcur[t] = rq[t];
+          if (g + 1u < ng)
+            load_res(row0 + 16, lane_active && col_lane + 16u * (g + 1u) < tile_rows, rq);
         }
         float y[16];
 #pragma unroll
@@ -480,7 +523,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
 #pragma unroll
           for (int t = 0; t < 4; ++t) {
             const uint32_t row = row0 + 4u * j4 + t;
-            if (row < n_out) *(uint32_t*)(a.out + (size_t)row * COUT + chq) = w[t];
+            if (in_tile && row < n_out) *(uint32_t*)(a.out + (size_t)row * COUT + chq) = w[t];
           }
         } else {
 #pragma unroll
@@ -490,7 +533,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
             uint32_t w0 = *(uint32_t*)&h0, w1 = *(uint32_t*)&h1;
             quad_transpose_h16(w0, w1, lane);
             const uint32_t row = row0 + 4u * t + j4;
-            if (row < n_out)
+            if (in_tile && row < n_out)
               *(uint2*)(a.out + ((size_t)row * COUT + chq) * out_b) = make_uint2(w0, w1);
           }
         }
@@ -528,7 +571,7 @@ int launch_one(const UmmaArgs& args, uint32_t launch_rows, cudaStream_t st) {
                                           (int)smem));
     if (dev >= 0 && dev < 64) attr_done[dev] = true;
   }
-  uint32_t tiles = (launch_rows + kTileRows - 1) / kTileRows;
+  uint32_t tiles = (launch_rows + 31) / 32;  // the kernel picks the tile height per launch
   int grid = (int)(tiles < (uint32_t)kSmCount ? (tiles ? tiles : 1u) : (uint32_t)kSmCount);
   conv_umma_kernel<INT8, RB, COUT><<<grid, kCtaThreads, smem, st>>>(args);
   SPCONVB_LAUNCH_CHECK();

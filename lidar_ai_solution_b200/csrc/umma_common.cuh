@@ -24,6 +24,8 @@ struct UmmaArgs {
   uint8_t* out;
   uint32_t* status;
   int kvol;
+  int w_rep;       // copies of each weight chunk along the 128 accumulator lanes (1..128/Cout)
+  int w_resident;  // 1: all chunks stay in shared memory for the whole launch; 0: streamed
   Epilogue ep;
 };
 
