@@ -436,11 +436,11 @@ def run_gpu(args, rank, world, local_rank):
 
 # DRAM bytes (read + write) of the convolution launches per algorithmic byte.  ncu cannot
 # capture the full frame within its size limits, so the frame's traffic is one captured
-# launch (profiles/conv_umma_int8_c64_170k.md: dram read + write = 29.43 MB for 40.23 MB of
+# launch (profiles/conv_umma_int8_c64_170k.md: dram read + write = 29.41 MB for 40.23 MB of
 # algorithmic bytes; the output is still in L2 when the launch ends) scaled to the frame's
 # algorithmic convolution bytes (704.4 MB on the default workload), traffic growing in
 # proportion to rows.
-CONV_DRAM_PER_ALGORITHMIC_BYTE = 0.7316
+CONV_DRAM_PER_ALGORITHMIC_BYTE = 0.731
 
 
 def main():
