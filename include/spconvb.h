@@ -107,6 +107,21 @@ SPCONVB_API int spconvb_subm_map_ranked(const int32_t* coords, const uint32_t* n
                                         const void* down_workspace, int32_t* map,
                                         uint32_t* status, void* stream);
 
+/* Map of an inverse (transposed) sparse convolution: the pairs of the strided
+ * rulebook built by spconvb_down_map with the same geometry, input and output
+ * swapped (the `inverse` argument of EngineBuilder::push_sparse_conv, engine.hpp:156;
+ * "SparseInverseConvolution", libraries/3DSparseConvolution/README.md:151).
+ * `coords` are the rows that were the INPUT of that spconvb_down_map call (they are the
+ * outputs here), `grid` their grid, `down_workspace` that call's workspace (still
+ * intact) and `cap_coarse` its cap_out.  map is [kvol][cap]: map[k][i] = row of the
+ * strided output that row i contributed to through tap k, or -1. */
+SPCONVB_API int spconvb_inverse_map(const int32_t* coords, const uint32_t* n_ptr, uint32_t cap,
+                                    uint32_t launch_rows, const int32_t grid[3], int32_t batch,
+                                    const int32_t ksize[3], const int32_t stride[3],
+                                    const int32_t pad[3], const int32_t dilation[3],
+                                    const void* down_workspace, uint32_t cap_coarse,
+                                    int32_t* map, uint32_t* status, void* stream);
+
 /* Output grid of a strided conv along one axis. */
 SPCONVB_API int32_t spconvb_out_extent(int32_t in, int32_t k, int32_t stride, int32_t pad,
                                        int32_t dilation);

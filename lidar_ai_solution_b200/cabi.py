@@ -52,6 +52,8 @@ SYMBOLS = {
                                    C.c_uint32, _VP, _VP, _VP]),
     "spconvb_subm_map_ranked": (C.c_int, [_VP, _VP, C.c_uint32, C.c_uint32, _I3, C.c_int32, _I3, _I3,
                                           _VP, _VP, _VP, _VP]),
+    "spconvb_inverse_map": (C.c_int, [_VP, _VP, C.c_uint32, C.c_uint32, _I3, C.c_int32, _I3, _I3, _I3,
+                                      _I3, _VP, C.c_uint32, _VP, _VP, _VP]),
     "spconvb_out_extent": (C.c_int32, [C.c_int32] * 5),
     "spconvb_down_workspace_bytes": (C.c_size_t, [_I3, C.c_int32]),
     "spconvb_down_map": (C.c_int, [_VP, _VP, C.c_uint32, C.c_uint32, _I3, C.c_int32, _I3, _I3, _I3,

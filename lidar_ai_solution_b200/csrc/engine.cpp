@@ -206,6 +206,7 @@ int Engine::compile(const Builder& b, int precision, uint32_t build_flags, cudaS
   // ---- walk the graph, emit steps
   std::vector<int> g2r(nt, -1);  // graph tensor -> runtime tensor
   std::vector<char> hash_emitted;
+  std::unordered_map<std::string, int> rule_by_name;  // strided rulebooks, for inverse convs
   struct ConvKey { int src, kind, ch; float s; int rt; };
   std::vector<ConvKey> converted;
 
@@ -326,9 +327,45 @@ int Engine::compile(const Builder& b, int precision, uint32_t build_flags, cudaS
         // --- rulebook (shared by structure)
         const int kvol = n.ksize[0] * n.ksize[1] * n.ksize[2];
         int rule = -1;
-        for (int r = 0; r < (int)rules.size(); ++r) {
+        if (n.inverse) {
+          // the pairs of an earlier strided conv, found by its rulebook name, with input and
+          // output swapped; the geometry is that conv's (an inverse conv module carries only
+          // the kernel size)
+          auto it = rule_by_name.find(n.rulebook);
+          if (n.rulebook.empty() || it == rule_by_name.end()) {
+            log_msg(LOG_ERROR, "conv '%s': inverse needs the rulebook of an earlier strided conv",
+                    n.name.c_str());
+            return SPCONVB_E_ARG;
+          }
+          const int fwd = it->second;
+          if (rules[fwd].out_cs != in_cs || rules[fwd].kvol != kvol) {
+            log_msg(LOG_ERROR, "conv '%s': input rows or kernel do not match rulebook '%s'",
+                    n.name.c_str(), n.rulebook.c_str());
+            return SPCONVB_E_ARG;
+          }
+          for (int r = 0; r < (int)rules.size(); ++r)
+            if (rules[r].inverse_of == fwd) rule = r;
+          if (rule < 0) {
+            Rule R = rules[fwd];
+            R.inverse_of = fwd;
+            R.in_cs = rules[fwd].out_cs;
+            R.out_cs = rules[fwd].in_cs;
+            R.map = nullptr;
+            R.ws = nullptr;
+            R.ws_bytes = 0;
+            rules.push_back(R);
+            rule = (int)rules.size() - 1;
+            Step s;
+            s.kind = Step::INV_MAP;
+            s.name = "inverse_map:" + n.rulebook;
+            s.rule = rule;
+            s.cs = R.out_cs;
+            steps.push_back(s);
+          }
+        }
+        for (int r = 0; r < (int)rules.size() && !n.inverse; ++r) {
           const Rule& R = rules[r];
-          if (R.subm == n.subm && R.in_cs == in_cs && same3(R.ksize, n.ksize) &&
+          if (R.inverse_of < 0 && R.subm == n.subm && R.in_cs == in_cs && same3(R.ksize, n.ksize) &&
               same3(R.dil, n.dil) && (n.subm || (same3(R.stride, n.stride) && same3(R.pad, n.pad))))
             rule = r;
         }
@@ -362,6 +399,7 @@ int Engine::compile(const Builder& b, int precision, uint32_t build_flags, cudaS
           s.cs = in_cs;
           steps.push_back(s);
         }
+        if (!n.subm && !n.inverse && !n.rulebook.empty()) rule_by_name[n.rulebook] = rule;
         // --- weights
         LayerWeights lw;
         {
@@ -594,7 +632,8 @@ int Engine::compile(const Builder& b, int precision, uint32_t build_flags, cudaS
     names_text += rt[r].name + "\n";
   }
   for (const Step& s : steps) {
-    static const char* kn[] = {"hash", "subm_map", "down_map", "convert", "conv", "add", "relu", "dense"};
+    static const char* kn[] = {"hash", "subm_map", "down_map", "convert", "conv", "add", "relu",
+                               "dense", "inverse_map"};
     char line[512];
     snprintf(line, sizeof(line),
              "%s %s rule=%d in_cs=%d out_cs=%d cin=%d cout=%d kvol=%d in=%s out=%s res=%d\n",
@@ -626,7 +665,7 @@ int Engine::prepare(const int32_t grid[3], int batch) {
       cs.cap = cs.bound ? cs.bound : 200000u;
     }
   for (auto& R : rules) {
-    if (R.subm) continue;
+    if (R.subm || R.inverse_of >= 0) continue;
     CoordSet& in = coordsets[R.in_cs];
     CoordSet& out = coordsets[R.out_cs];
     unsigned long long cells = batch;
@@ -658,7 +697,7 @@ int Engine::prepare(const int32_t grid[3], int batch) {
     zoff += align256(sizeof(uint64_t) * (size_t)cs.slots);
   }
   for (size_t r = 0; r < rules.size(); ++r) {
-    if (rules[r].subm) continue;
+    if (rules[r].subm || rules[r].inverse_of >= 0) continue;
     ws_off[r] = zoff;
     // only the bitmap (first third of the workspace) must be zero, but the
     // rest is small next to it and one memset is cheaper than two
@@ -687,7 +726,7 @@ int Engine::prepare(const int32_t grid[3], int batch) {
     if ((rc = dev_alloc(&p, sizeof(int32_t) * (size_t)R.kvol * coordsets[R.out_cs].cap)) != SPCONVB_OK)
       return rc;
     R.map = (int32_t*)p;
-    R.ws = R.subm ? nullptr : (void*)(zb + ws_off[r]);
+    R.ws = (R.subm || R.inverse_of >= 0) ? nullptr : (void*)(zb + ws_off[r]);
   }
 
   // ---- feature buffers, reused by liveness unless every tensor must stay readable
@@ -793,6 +832,16 @@ int Engine::forward(const void* features, const int32_t* indices, uint32_t cap_r
                               ci.table, ci.slots, R.ws, co.coords, co.n_ptr, co.cap, R.map,
                               co.table, co.slots, SPCONVB_FLAG_PREZEROED, status, st);
         last_launches += 4;
+        break;
+      }
+      case Step::INV_MAP: {
+        const Rule& R = rules[s.rule];
+        const Rule& F = rules[R.inverse_of];
+        rc = spconvb_inverse_map(cs_coords(R.out_cs), cs_n(R.out_cs), coordsets[R.out_cs].cap,
+                                 cs_launch(R.out_cs), coordsets[R.out_cs].grid, batch, F.ksize,
+                                 F.stride, F.pad, F.dil, F.ws, coordsets[F.out_cs].cap, R.map,
+                                 status, st);
+        last_launches += 1;
         break;
       }
       case Step::CONVERT:

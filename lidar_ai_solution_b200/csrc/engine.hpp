@@ -34,6 +34,7 @@ struct GNode {
   int ksize[3] = {1, 1, 1}, stride[3] = {1, 1, 1}, pad[3] = {0, 0, 0}, dil[3] = {1, 1, 1};
   float in_dr = 0.f;
   bool subm = false;
+  bool inverse = false;  // runs over the pairs of the strided rulebook named `rulebook`, swapped
   uint32_t out_bound = 0, fixed_launch = 0;
   std::string rulebook;
   int prec = SPCONVB_PRECISION_FP16, out_prec = SPCONVB_PRECISION_FP16;
@@ -83,6 +84,7 @@ struct Rule {
   int ksize[3], stride[3], pad[3], dil[3];
   int kvol = 1;
   int in_cs = -1, out_cs = -1;
+  int inverse_of = -1;       // >= 0: the strided rule whose pairs this rule swaps
   int32_t* map = nullptr;
   void* ws = nullptr;
   size_t ws_bytes = 0;
@@ -112,7 +114,7 @@ struct LayerWeights {
 };
 
 struct Step {
-  enum Kind { HASH, SUBM_MAP, DOWN_MAP, CONVERT, CONV, ADD, RELU, DENSE } kind;
+  enum Kind { HASH, SUBM_MAP, DOWN_MAP, CONVERT, CONV, ADD, RELU, DENSE, INV_MAP } kind;
   std::string name;
   int cs = -1, rule = -1;
   int in0 = -1, in1 = -1, out = -1;  // runtime tensors

@@ -45,10 +45,6 @@ int spconvb_builder_sparse_conv(spconvb_builder* b, const char* name, int x,
                                 const char* output_name, int32_t inverse) {
   if (bad(b, x) || !weight || !weight_shape || !kernel_size || !stride || !padding || !dilation)
     return SPCONVB_E_ARG;
-  if (inverse) {
-    log_msg(LOG_ERROR, "conv '%s': inverse convolution is not implemented", nz(name));
-    return SPCONVB_E_UNSUPPORTED;
-  }
   const std::string act = nz(activation);
   if (!act.empty() && act != "ReLU" && act != "None") {
     log_msg(LOG_ERROR, "conv '%s': activation '%s' is not supported", nz(name), act.c_str());
@@ -80,6 +76,7 @@ int spconvb_builder_sparse_conv(spconvb_builder* b, const char* name, int x,
   n.relu_act = act == "ReLU";
   n.in_dr = input_dynamic_range;
   n.subm = submanifold != 0;
+  n.inverse = inverse != 0;
   n.out_bound = max_output_points ? max_output_points : 150000u;
   n.fixed_launch = fixed_launch_points;
   n.rulebook = nz(rulebook);

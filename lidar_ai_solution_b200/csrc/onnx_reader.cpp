@@ -330,10 +330,7 @@ int load_onnx(const char* path, uint32_t fixed_launch_points, Builder* out) {
       if (n.attrs.count("rulebook")) g.rulebook = attr(n, "rulebook").s;
       g.prec = prec_of(attr(n, "precision").s);
       g.out_prec = prec_of(attr(n, "output_precision").s);
-      if (attr(n, "inverse").i != 0) {
-        log_msg(LOG_ERROR, "conv '%s': inverse convolution is not implemented", n.name.c_str());
-        return SPCONVB_E_UNSUPPORTED;
-      }
+      g.inverse = attr(n, "inverse").i != 0;
     } else if (n.op == "Add" || n.op == "QuantAdd") {
       if (n.in.size() < 2) return SPCONVB_E_PARSE;
       g.op = OP_ADD;

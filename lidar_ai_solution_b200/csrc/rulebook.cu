@@ -455,6 +455,74 @@ int spconvb_subm_map_ranked(const int32_t* coords, const uint32_t* n_ptr, uint32
   return SPCONVB_OK;
 }
 
+// Map of an inverse (transposed) convolution: it runs over the pairs of a strided
+// rulebook with input and output swapped, so its outputs are that rulebook's input rows
+// and map[k][i] is the strided output row that input row i reaches through tap k.  One
+// thread per (row, tap): the cell arithmetic of for_each_output for one tap, then a rank
+// lookup in the bitmap the strided rulebook left behind.
+__global__ void inverse_map_kernel(const int4* __restrict__ coords, const uint32_t* n_ptr,
+                                   uint32_t cap, Grid3 gin, Grid3 gout, Kernel3 kr, int kvol,
+                                   DownWs ws, uint32_t cap_coarse, int32_t* __restrict__ map) {
+  const uint32_t n = min(*n_ptr, cap);
+  const unsigned long long work = (unsigned long long)n * kvol;
+  for (unsigned long long idx = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
+       idx < work; idx += (unsigned long long)gridDim.x * blockDim.x) {
+    const uint32_t row = (uint32_t)(idx / kvol);
+    const int k = (int)(idx - (unsigned long long)row * kvol);
+    const int k2 = k % kr.k[2], k1 = (k / kr.k[2]) % kr.k[1], k0 = k / (kr.k[2] * kr.k[1]);
+    const int4 c = __ldg(coords + row);
+    int32_t o = -1;
+    if ((unsigned)c.x < (unsigned)gin.batch) {
+      const int v0 = c.y + kr.p[0] - k0 * kr.d[0];
+      const int v1 = c.z + kr.p[1] - k1 * kr.d[1];
+      const int v2 = c.w + kr.p[2] - k2 * kr.d[2];
+      if (v0 >= 0 && v1 >= 0 && v2 >= 0 && v0 % kr.s[0] == 0 && v1 % kr.s[1] == 0 &&
+          v2 % kr.s[2] == 0) {
+        const int o0 = v0 / kr.s[0], o1 = v1 / kr.s[1], o2 = v2 / kr.s[2];
+        if (o0 < gout.g[0] && o1 < gout.g[1] && o2 < gout.g[2])
+          o = rank_lookup(ws.bitmap, ws.prefix, voxel_key(c.x, o0, o1, o2, gout), cap_coarse);
+      }
+    }
+    map[(size_t)k * cap + row] = o;
+  }
+}
+
+int spconvb_inverse_map(const int32_t* coords, const uint32_t* n_ptr, uint32_t cap,
+                        uint32_t launch_rows, const int32_t grid[3], int32_t batch,
+                        const int32_t ksize[3], const int32_t stride[3], const int32_t pad[3],
+                        const int32_t dilation[3], const void* down_workspace,
+                        uint32_t cap_coarse, int32_t* map, uint32_t* status, void* stream) {
+  (void)status;
+  if (!coords || !n_ptr || !grid || !ksize || !stride || !pad || !dilation || !down_workspace ||
+      !map)
+    return SPCONVB_E_ARG;
+  if (!grid_fits(grid, batch)) return SPCONVB_E_RANGE;
+  Kernel3 kr;
+  int32_t og[3];
+  for (int a2 = 0; a2 < 3; ++a2) {
+    if (ksize[a2] < 1 || stride[a2] < 1 || pad[a2] < 0 || dilation[a2] < 1) return SPCONVB_E_ARG;
+    kr.k[a2] = ksize[a2]; kr.s[a2] = stride[a2]; kr.p[a2] = pad[a2]; kr.d[a2] = dilation[a2];
+    og[a2] = spconvb_out_extent(grid[a2], ksize[a2], stride[a2], pad[a2], dilation[a2]);
+    if (og[a2] < 1) return SPCONVB_E_ARG;
+  }
+  const int kvol = ksize[0] * ksize[1] * ksize[2];
+  if (kvol > 65535) return SPCONVB_E_ARG;
+  if (!grid_fits(og, batch)) return SPCONVB_E_RANGE;
+  DownWs ws;
+  ws.words = down_words(og, batch);
+  ws.blocks = (ws.words + kScanWordsPerBlock - 1) / kScanWordsPerBlock;
+  ws.bitmap = (uint32_t*)down_workspace;
+  ws.prefix = ws.bitmap + ws.words;
+  ws.block_sums = ws.prefix + ws.words;
+  if (launch_rows == 0 || launch_rows > cap) launch_rows = cap;
+  inverse_map_kernel<<<flat_blocks((unsigned long long)launch_rows * kvol), kThreads, 0,
+                       (cudaStream_t)stream>>>((const int4*)coords, n_ptr, cap,
+                                               make_grid(grid, batch), make_grid(og, batch), kr,
+                                               kvol, ws, cap_coarse, map);
+  SPCONVB_LAUNCH_CHECK();
+  return SPCONVB_OK;
+}
+
 size_t spconvb_down_workspace_bytes(const int32_t out_grid[3], int32_t batch) {
   if (!out_grid || !grid_fits(out_grid, batch)) return 0;
   size_t words = down_words(out_grid, batch);

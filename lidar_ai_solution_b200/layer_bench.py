@@ -11,6 +11,10 @@ algorithmic bytes and useful ops of the launch, achieved GB/s and TOPS, and the
 fraction of the measured HBM copy bandwidth (MEASURED_PEAKS.json when present).
 The rulebook kernels are timed the same way.  This is the per-layer view the
 reference's `infer --profiling` gives for a whole model.
+
+    python -m lidar_ai_solution_b200.layer_bench --voxelizer 100000 200000 300000 [--fp16]
+
+times the voxelizer on raw sweeps of that many points instead.
 """
 from __future__ import annotations
 
@@ -93,6 +97,43 @@ def run_case(c, n, grid, fp16, reps, flush, seed=0):
             "map_gbs": (16 * n + 4 * 27 * n) / us_map / 1e3}
 
 
+def run_voxelizer(n_points, fp16, reps, flush, seed=0):
+    """One raw sweep through the voxelizer (CenterPoint ranges: 1440x1440x40 voxels of
+    0.075 x 0.075 x 0.2 m, at most 10 points per voxel, 160 000 voxels)."""
+    pts = scenes.make_points(n_points, seed)
+    if fp16:
+        pts = pts.astype(np.float16)
+    dev = torch.from_numpy(pts).cuda()
+    params = ops.voxel_params(scenes.CENTERPOINT_RANGE, scenes.CENTERPOINT_VOXEL, (1440, 1440, 40),
+                              5, 1 if fp16 else 0, 10, 160000, 0)
+    st = ops.new_status()
+    lib = ops.cabi.lib()
+    import ctypes as C
+    ws = torch.empty(max(256, lib.spconvb_voxelize_workspace_bytes(C.byref(params), n_points)),
+                     dtype=torch.uint8, device="cuda")
+    feat = torch.zeros((160000, 5), dtype=torch.float16, device="cuda")
+    idx = torch.zeros((160000, 4), dtype=torch.int32, device="cuda")
+    n_ptr = torch.zeros(1, dtype=torch.int32, device="cuda")
+
+    def vox():
+        ops.cabi.check(lib.spconvb_voxelize(
+            C.byref(params), C.c_void_p(dev.data_ptr()), n_points, C.c_void_p(ws.data_ptr()),
+            C.c_void_p(feat.data_ptr()), C.c_void_p(idx.data_ptr()), C.c_void_p(n_ptr.data_ptr()),
+            C.c_void_p(st.data_ptr()), C.c_void_p(torch.cuda.current_stream().cuda_stream)),
+            "voxelize")
+
+    vox()
+    torch.cuda.synchronize()
+    n = int(n_ptr.item())
+    us = _time(vox, reps, flush)
+    nbytes = n_points * 5 * (2 if fp16 else 4) + n * (5 * 2 + 16)
+    peak, src = _peak_gbs()
+    return {"kernel": "voxelize", "points": n_points, "points_dtype": "fp16" if fp16 else "fp32",
+            "voxels": n, "us": us, "algorithmic_bytes": nbytes, "achieved_gbs": nbytes / us / 1e3,
+            "hbm_frac": nbytes / us / 1e3 / peak, "hbm_peak_gbs": peak, "peak_source": src,
+            "points_per_s": n_points / us * 1e6}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--channels", type=int, nargs="+", default=[16, 32, 64, 128])
@@ -101,8 +142,14 @@ def main():
     ap.add_argument("--fp16", action="store_true")
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--voxelizer", type=int, nargs="*", default=None, metavar="POINTS",
+                    help="time the voxelizer on sweeps of this many points instead")
     args = ap.parse_args()
     flush = None if args.no_flush else torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    if args.voxelizer is not None:
+        for n in (args.voxelizer or [100000, 200000, 300000]):
+            print(json.dumps(run_voxelizer(n, args.fp16, args.reps, flush)), flush=True)
+        return
     for c in args.channels:
         for n in args.voxels:
             print(json.dumps(run_case(c, n, tuple(args.grid), args.fp16, args.reps, flush)),

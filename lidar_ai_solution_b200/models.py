@@ -127,6 +127,33 @@ def single_layer(cin: int, cout: int, seed: int = 0, subm: bool = True, output_b
             "nodes": nodes, "roles": {"conv_input": [0]}, "in_channels": cin}
 
 
+def encoder_decoder(channels: int = 16, seed: int = 0, in_channels: int = 16,
+                    output_bound=200000):
+    """A segmentation-style block: SubM conv, stride-2 conv (rulebook "down0"), SubM conv on
+    the coarse rows, SparseInverseConvolution back onto the fine rows through the same
+    rulebook, Add with the skip connection, ReLU.  Both the fine sum and the coarse tensor
+    are graph outputs (sparse, two outputs)."""
+    rng = np.random.default_rng(seed)
+    ids, nodes, counter = _Ids(), [], [0, 0]
+    c = channels
+    x0 = _conv(ids, rng, nodes, "0", in_channels, c, (3, 3, 3), (1, 1, 1), (1, 1, 1), True,
+               "subm0", "ReLU", counter, output_bound)
+    d = _conv(ids, rng, nodes, x0, c, 2 * c, (3, 3, 3), (2, 2, 2), (1, 1, 1), False, "down0",
+              "ReLU", counter, output_bound)
+    e = _conv(ids, rng, nodes, d, 2 * c, 2 * c, (3, 3, 3), (1, 1, 1), (1, 1, 1), True, "subm1",
+              "ReLU", counter, output_bound)
+    u = _conv(ids, rng, nodes, e, 2 * c, c, (3, 3, 3), (2, 2, 2), (1, 1, 1), False, "down0",
+              "None", counter, output_bound)
+    nodes[-1]["inverse"] = 1
+    s = ids.new()
+    nodes.append({"op": "add", "name": "add0", "a": u, "b": x0, "out": s})
+    r = ids.new()
+    nodes.append({"op": "relu", "name": "relu0", "x": s, "out": r})
+    return {"kind": "encoder_decoder", "inputs": [("0", [1, in_channels])],
+            "outputs": [(r, [1, c]), (e, [1, 2 * c])], "nodes": nodes,
+            "roles": {"conv_input": [0]}, "in_channels": in_channels}
+
+
 def quantize(model: dict, ranges: dict, kind: str | None = None) -> dict:
     """Attach the int8 attributes.  ``ranges`` maps tensor id -> absmax seen in
     calibration (plain absmax on one frame).  Weight ranges are per output

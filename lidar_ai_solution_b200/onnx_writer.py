@@ -102,7 +102,8 @@ def serialize(model: dict) -> bytes:
                 "out_channels": int(nd["weight"].shape[0]),
                 "kernel_size": list(nd["kernel_size"]), "output_bound": int(nd["output_bound"]),
                 "stride": list(nd["stride"]), "dilation": list(nd["dilation"]),
-                "padding": list(nd["padding"]), "transposed": 0, "inverse": 0,
+                "padding": list(nd["padding"]), "transposed": 0,
+                "inverse": int(nd.get("inverse", 0)),
                 "subm": int(nd["subm"]), "rulebook": nd.get("rulebook", ""),
                 "activation": nd["activation"],
             }

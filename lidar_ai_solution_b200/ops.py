@@ -104,6 +104,20 @@ def subm_map_ranked(coords, n_ptr, grid, ws, ksize=(3, 3, 3), dilation=(1, 1, 1)
     return m
 
 
+def inverse_map(coords, n_ptr, grid, ws, cap_coarse, ksize, stride, pad, dilation=(1, 1, 1),
+                batch=1, status=None, launch_rows=0):
+    """Map of the inverse conv of a strided rulebook: ``coords`` are the rows that went INTO
+    ``down_map`` (with ``return_ws=True``), ``ws`` its workspace, ``cap_coarse`` its cap_out."""
+    cap = coords.shape[0]
+    kvol = int(np.prod(ksize))
+    m = torch.empty((kvol, cap), dtype=torch.int32, device=coords.device)
+    cabi.check(cabi.lib().spconvb_inverse_map(_ptr(coords), _ptr(n_ptr), cap, launch_rows,
+                                              cabi.i3(grid), batch, cabi.i3(ksize), cabi.i3(stride),
+                                              cabi.i3(pad), cabi.i3(dilation), _ptr(ws), cap_coarse,
+                                              _ptr(m), _ptr(status), _stream()), "inverse_map")
+    return m
+
+
 class ConvWeights:
     """Device copies of one layer's parameters in both kernel formats."""
 

@@ -84,13 +84,28 @@ def run(model, features, coords, grid, precision="fp16"):
                                      grid=list(grid), kind="f16", dr=0.0)}
     dense = {}
     rule_cache = {}
+    named_rules = {}
     for n in model["nodes"]:
         op = n["op"]
         if op == "conv":
             src = T[n["x"]]
             compute = _eff(precision, n.get("precision", "fp16"))
             key = (id(src["coords"]), tuple(n["kernel_size"]), tuple(n["stride"]),
-                   tuple(n["padding"]), tuple(n["dilation"]), n["subm"])
+                   tuple(n["padding"]), tuple(n["dilation"]), n["subm"], bool(n.get("inverse")))
+            if n.get("inverse"):
+                # SparseInverseConvolution (engine.hpp:156 `inverse`): the pairs of the strided
+                # rulebook with the same `rulebook` key, input and output swapped; the outputs
+                # are that rulebook's input rows
+                fwd = named_rules[n["rulebook"]]
+                if fwd["coarse"] is not src["coords"]:
+                    raise ValueError("inverse conv %s: input is not the output of rulebook %s"
+                                     % (n["name"], n["rulebook"]))
+                inv = np.full((fwd["map"].shape[0], len(fwd["fine"])), -1, np.int32)
+                for k in range(fwd["map"].shape[0]):
+                    rows = fwd["map"][k, :fwd["n_coarse"]]
+                    o = np.nonzero(rows >= 0)[0]
+                    inv[k, rows[o]] = o
+                rule_cache[key] = (fwd["fine"], inv, list(fwd["fine_grid"]), len(fwd["fine"]))
             if key not in rule_cache:
                 if n["subm"]:
                     m, _ = orc.subm_map(src["coords"], src["grid"], n["kernel_size"], n["dilation"])
@@ -100,6 +115,9 @@ def run(model, features, coords, grid, precision="fp16"):
                                                        n["stride"], n["padding"], n["dilation"],
                                                        cap=n.get("output_bound"))
                     rule_cache[key] = (oc, m, og, len(oc))
+                    if n.get("rulebook"):
+                        named_rules[n["rulebook"]] = dict(fine=src["coords"], fine_grid=src["grid"],
+                                                          coarse=oc, map=m, n_coarse=n_out)
             oc, m, og, n_out = rule_cache[key]
             w16 = np.ascontiguousarray(n["weight"], np.float16)
             cout, cin = w16.shape[0], w16.shape[-1]

@@ -373,3 +373,73 @@ def test_infer_cli_runs_every_mode(tmp_path, capsys):
     assert "Stress test done:" in capsys.readouterr().out
     assert infer.main(base + ["--search_best_perf"]) == 0
     assert "Best configuration found" in capsys.readouterr().out
+
+
+# --------------------------------------------- inverse convolution, two sparse outputs
+def _encoder_decoder_case(n=7000, seed=11):
+    grid = (21, 200, 200)
+    coords = scenes.make_coords(n, grid, seed)
+    feats = np.random.default_rng(seed).standard_normal((n, 16)).astype(np.float16)
+    model = models.encoder_decoder(16, seed=seed, in_channels=16, output_bound=60000)
+    return model, feats, coords, grid
+
+
+@pytest.mark.parametrize("simt", [True, False])
+def test_inverse_conv_fp16_matches_oracle(simt):
+    """SparseInverseConvolution (`inverse` of push_sparse_conv, engine.hpp:156): the decoder
+    conv runs over the pairs of the stride-2 rulebook "down0" swapped, lands on the rows the
+    encoder started from and is added to the skip tensor.  CUDA-core path: every tensor
+    identical to the oracle; tensor-core path: within 1e-2 of the layer's magnitude."""
+    eng = _engine_mod()
+    model, feats, coords, grid = _encoder_decoder_case()
+    outs, T = graph_oracle.run(model, feats, coords, grid, "fp16")
+    flags = eng.BUILD_KEEP_TENSORS | eng.BUILD_NO_FUSION | (eng.BUILD_FORCE_SIMT if simt else 0)
+    e = eng.Engine.from_model(model, eng.PRECISION_FP16, flags)
+    assert e.num_outputs() == 2
+    e.forward(_dev(feats), _dev(coords), grid)
+    torch.cuda.synchronize()
+    assert e.status()[0] == 0
+    _compare_all(e, T, exact=simt)
+    inv = [nd for nd in model["nodes"] if nd.get("inverse")][0]
+    got = e.tensor(inv["out"])
+    assert got["n"] == len(coords)                      # back on the fine rows
+    assert "inverse_map:down0" in e.describe()
+
+
+@pytest.mark.parametrize("fusion", [False, True])
+def test_inverse_conv_int8_exact(fusion):
+    eng = _engine_mod()
+    model, feats, coords, grid = _encoder_decoder_case(seed=12)
+    ranges = eng.calibrate(model, _dev(feats), _dev(coords), grid)
+    qm = models.quantize(model, ranges)
+    outs, T = graph_oracle.run(qm, feats, coords, grid, "int8")
+    flags = eng.BUILD_FORCE_SIMT | (0 if fusion else eng.BUILD_KEEP_TENSORS | eng.BUILD_NO_FUSION)
+    e = eng.Engine.from_model(qm, eng.PRECISION_INT8, flags)
+    e.forward(_dev(feats), _dev(coords), grid)
+    torch.cuda.synchronize()
+    assert e.status()[0] == 0
+    if not fusion:
+        _compare_all(e, T, exact=True)
+    for (tid, _), ref in zip(qm["outputs"], outs):
+        got = e.tensor(tid)
+        n = got["n"]
+        assert n == len(ref)
+        assert np.array_equal(got["features"][:n].cpu().numpy().view(np.uint8), ref.view(np.uint8))
+    # the tensor-core kernels see the same int8 operands: identical too
+    e2 = eng.Engine.from_model(qm, eng.PRECISION_INT8, 0)
+    e2.forward(_dev(feats), _dev(coords), grid)
+    torch.cuda.synchronize()
+    for (tid, _), ref in zip(qm["outputs"], outs):
+        got = e2.tensor(tid)
+        assert np.array_equal(got["features"][:got["n"]].cpu().numpy().view(np.uint8),
+                              ref.view(np.uint8))
+
+
+def test_inverse_conv_needs_its_rulebook():
+    eng = _engine_mod()
+    model, feats, coords, grid = _encoder_decoder_case()
+    bad = dict(model)
+    bad["nodes"] = [dict(nd) for nd in model["nodes"]]
+    [nd for nd in bad["nodes"] if nd.get("inverse")][0]["rulebook"] = "nowhere"
+    with pytest.raises(RuntimeError):
+        eng.Engine.from_model(bad, eng.PRECISION_FP16, 0)

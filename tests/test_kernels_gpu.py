@@ -431,3 +431,37 @@ def test_voxelizer_max_voxels_clips():
     assert int(st.cpu().numpy()[0]) & cabi.ST_OVERFLOW
     assert np.array_equal(idx.cpu().numpy(), rc)
     assert np.array_equal(feat.cpu().numpy().view(np.uint16), rf.view(np.uint16))
+
+
+def test_inverse_map_is_the_strided_map_with_rows_swapped():
+    """spconvb_inverse_map: map[k][i] = o exactly for the pairs (k, i, o) of the strided
+    rulebook (oracle down_map), -1 elsewhere."""
+    ops = _ops()
+    grid, n = (21, 180, 180), 15000
+    coords = scenes.make_coords(n, grid, 31)
+    ks, st_, pd = (3, 3, 3), (2, 2, 2), (1, 1, 1)
+    roc, rdm, _, og, rn = orc.down_map(coords, grid, ks, st_, pd)
+    ref = np.full((27, n), -1, np.int32)
+    for k in range(27):
+        o = np.nonzero(rdm[k, :rn] >= 0)[0]
+        ref[k, rdm[k, o]] = o
+    dc, n_ptr, st = _dev(coords), ops.device_count(n), ops.new_status()
+    oc, n_out, dm, _, _, ws = ops.down_map(dc, n_ptr, grid, None, ks, st_, pd, status=st,
+                                           want_table=False, return_ws=True)
+    inv = ops.inverse_map(dc, n_ptr, grid, ws, oc.shape[0], ks, st_, pd, status=st)
+    torch.cuda.synchronize()
+    _status_ok(st)
+    assert int(n_out.item()) == rn
+    assert np.array_equal(inv.cpu().numpy(), ref)
+    # asymmetric geometry: kernel (3,1,1), stride (2,1,1), no padding
+    ks, st_, pd = (3, 1, 1), (2, 1, 1), (0, 0, 0)
+    roc, rdm, _, og, rn = orc.down_map(coords, grid, ks, st_, pd)
+    ref = np.full((3, n), -1, np.int32)
+    for k in range(3):
+        o = np.nonzero(rdm[k, :rn] >= 0)[0]
+        ref[k, rdm[k, o]] = o
+    oc, n_out, dm, _, _, ws = ops.down_map(dc, n_ptr, grid, None, ks, st_, pd, status=st,
+                                           want_table=False, return_ws=True)
+    inv = ops.inverse_map(dc, n_ptr, grid, ws, oc.shape[0], ks, st_, pd, status=st)
+    torch.cuda.synchronize()
+    assert np.array_equal(inv.cpu().numpy(), ref)

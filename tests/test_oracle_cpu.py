@@ -159,3 +159,29 @@ def test_graph_oracle_int8_matches_float_model_closely():
     # a loader precision of fp16 ignores the int8 attributes
     f_outs, _ = graph_oracle.run(qm, feats, coords, grid, "fp16")
     assert np.array_equal(f_outs[0].view(np.uint16), outs[0].view(np.uint16))
+
+
+def test_oracle_inverse_conv_equals_dense_transposed_conv():
+    """The inverse conv of the graph oracle (pairs of the strided rulebook swapped, same tap
+    index) is a dense conv_transpose3d evaluated at the fine active sites."""
+    torch = pytest.importorskip("torch")
+    from lidar_ai_solution_b200 import models
+    grid = (9, 12, 10)
+    coords = scenes.make_coords(300, grid, 1)
+    m = models.encoder_decoder(8, seed=2, in_channels=8, output_bound=5000)
+    feats = np.random.default_rng(0).standard_normal((300, 8)).astype(np.float16)
+    _, T = graph_oracle.run(m, feats, coords, grid, "fp16")
+    inv = [n for n in m["nodes"] if n.get("inverse")][0]
+    e, u = T[inv["x"]], T[inv["out"]]
+    assert np.array_equal(u["coords"], coords) and list(u["grid"]) == list(grid)
+    og = e["grid"]
+    xd = torch.zeros((1, e["feat"].shape[1], *og), dtype=torch.float64)
+    for r, (b, z, y, x) in enumerate(e["coords"]):
+        xd[0, :, z, y, x] = torch.from_numpy(e["feat"][r].astype(np.float64))
+    w = torch.from_numpy(inv["weight"].astype(np.float64)).permute(4, 0, 1, 2, 3).contiguous()
+    pad_out = [g - ((o - 1) * 2 - 2 + 3) for g, o in zip(grid, og)]
+    yd = torch.nn.functional.conv_transpose3d(xd, w, stride=2, padding=1, output_padding=pad_out)
+    ref = np.stack([yd[0, :, z, y, x].numpy() + inv["bias"].astype(np.float64)
+                    for (b, z, y, x) in coords])
+    got = u["feat"].astype(np.float64)
+    assert np.abs(got - ref).max() <= 2e-3 * np.abs(ref).max()
