@@ -12,7 +12,8 @@ from lidar_ai_solution_b200 import models, onnx_writer, scenes
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 LIB = os.path.join(ROOT, "lidar_ai_solution_b200", "lib")
-REF = "/root/reference"
+# the reference checkout: $SPCONV_REFERENCE_ROOT, else a "reference" directory beside this repo
+REF = os.environ.get("SPCONV_REFERENCE_ROOT", os.path.join(os.path.dirname(ROOT), "reference"))
 NVCC = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
 
 pytestmark = pytest.mark.skipif(not os.path.exists(NVCC), reason="nvcc not available")

@@ -35,9 +35,9 @@ def test_rulebook_counts_of_reference_frames(golden_dir, name, key):
     assert grid == [2, 180, 180]   # 128 channels x 2 = the 256-channel BEV map
 
 
-def test_survey_figures_for_the_centerpoint_frame(golden_dir):
+def test_known_counts_for_the_centerpoint_frame(golden_dir):
     """The published frame: 79 745 voxels, 591 581 SubM pairs, 69 276 voxels after the first
-    stride-2 conv (figures computed independently when the reference was surveyed)."""
+    stride-2 conv (figures computed independently with a NumPy restatement)."""
     gold = json.load(open(os.path.join(golden_dir, "fixture_counts.json")))["centerpoint"]
     assert [g["n"] for g in gold] == [79745, 69276, 29723, 10335]
     assert [g["subm_pairs"] for g in gold] == [591581, 969672, 483025, 172003]
