@@ -89,6 +89,20 @@ __host__ __device__ inline uint32_t down_words(const int32_t og[3], int batch) {
   return (uint32_t)((cells + 31) / 32);
 }
 
+// The output cell that input coordinate c reaches through tap k of a strided conv, if any.
+__device__ __forceinline__ bool tap_output_cell(const int4 c, int k, const Grid3& gout,
+                                                const Kernel3& kr, uint32_t* cell) {
+  const int k2 = k % kr.k[2], k1 = (k / kr.k[2]) % kr.k[1], k0 = k / (kr.k[2] * kr.k[1]);
+  const int v0 = c.y + kr.p[0] - k0 * kr.d[0];
+  const int v1 = c.z + kr.p[1] - k1 * kr.d[1];
+  const int v2 = c.w + kr.p[2] - k2 * kr.d[2];
+  if (v0 < 0 || v1 < 0 || v2 < 0 || v0 % kr.s[0] || v1 % kr.s[1] || v2 % kr.s[2]) return false;
+  const int o0 = v0 / kr.s[0], o1 = v1 / kr.s[1], o2 = v2 / kr.s[2];
+  if (o0 >= gout.g[0] || o1 >= gout.g[1] || o2 >= gout.g[2]) return false;
+  *cell = voxel_key(c.x, o0, o1, o2, gout);
+  return true;
+}
+
 // Visits the output cells one input row reaches: for every axis only the taps with
 // (c + pad - k*dil) divisible by the stride and inside the output grid survive, so
 // the nest below does ~14 divisions per row instead of 81, and `visit` runs once
@@ -286,7 +300,7 @@ __global__ void hash_rows_kernel(const int4* __restrict__ coords, const uint32_t
 
 // Submanifold map of a coordinate set that came out of down_map: neighbours are
 // found by rank in that set's bitmap, no hash table involved.  One thread per
-// (row, tap); the three taps along the last axis hit the same or adjacent words.
+// (row, tap).
 __global__ void subm_ranked_kernel(const int4* __restrict__ coords, const uint32_t* n_ptr,
                                    uint32_t cap, Grid3 g, Kernel3 kr, int kvol, DownWs ws,
                                    int32_t* __restrict__ map) {
@@ -294,9 +308,10 @@ __global__ void subm_ranked_kernel(const int4* __restrict__ coords, const uint32
   const unsigned long long work = (unsigned long long)n * kvol;
   for (unsigned long long idx = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
        idx < work; idx += (unsigned long long)gridDim.x * blockDim.x) {
-    // consecutive threads take consecutive taps of one row: their cells are neighbours
-    const uint32_t row = (uint32_t)(idx / kvol);
-    const int k = (int)(idx - (unsigned long long)row * kvol);
+    // consecutive threads take consecutive rows of one tap: the map stores coalesce, and
+    // rows are in cell order, so their lookups fall into the same or adjacent bitmap words
+    const int k = (int)(idx / n);
+    const uint32_t row = (uint32_t)(idx - (unsigned long long)k * n);
     const int k2 = k % kr.k[2], k1 = (k / kr.k[2]) % kr.k[1], k0 = k / (kr.k[2] * kr.k[1]);
     const int d0 = (k0 - kr.k[0] / 2) * kr.d[0];
     const int d1 = (k1 - kr.k[1] / 2) * kr.d[1];
@@ -458,7 +473,7 @@ int spconvb_subm_map_ranked(const int32_t* coords, const uint32_t* n_ptr, uint32
 // Map of an inverse (transposed) convolution: it runs over the pairs of a strided
 // rulebook with input and output swapped, so its outputs are that rulebook's input rows
 // and map[k][i] is the strided output row that input row i reaches through tap k.  One
-// thread per (row, tap): the cell arithmetic of for_each_output for one tap, then a rank
+// thread per (row, tap): the strided conv's cell arithmetic for that tap, then a rank
 // lookup in the bitmap the strided rulebook left behind.
 __global__ void inverse_map_kernel(const int4* __restrict__ coords, const uint32_t* n_ptr,
                                    uint32_t cap, Grid3 gin, Grid3 gout, Kernel3 kr, int kvol,
@@ -467,22 +482,13 @@ __global__ void inverse_map_kernel(const int4* __restrict__ coords, const uint32
   const unsigned long long work = (unsigned long long)n * kvol;
   for (unsigned long long idx = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
        idx < work; idx += (unsigned long long)gridDim.x * blockDim.x) {
-    const uint32_t row = (uint32_t)(idx / kvol);
-    const int k = (int)(idx - (unsigned long long)row * kvol);
-    const int k2 = k % kr.k[2], k1 = (k / kr.k[2]) % kr.k[1], k0 = k / (kr.k[2] * kr.k[1]);
+    const int k = (int)(idx / n);  // rows fastest: coalesced stores of map[k][row]
+    const uint32_t row = (uint32_t)(idx - (unsigned long long)k * n);
     const int4 c = __ldg(coords + row);
     int32_t o = -1;
-    if ((unsigned)c.x < (unsigned)gin.batch) {
-      const int v0 = c.y + kr.p[0] - k0 * kr.d[0];
-      const int v1 = c.z + kr.p[1] - k1 * kr.d[1];
-      const int v2 = c.w + kr.p[2] - k2 * kr.d[2];
-      if (v0 >= 0 && v1 >= 0 && v2 >= 0 && v0 % kr.s[0] == 0 && v1 % kr.s[1] == 0 &&
-          v2 % kr.s[2] == 0) {
-        const int o0 = v0 / kr.s[0], o1 = v1 / kr.s[1], o2 = v2 / kr.s[2];
-        if (o0 < gout.g[0] && o1 < gout.g[1] && o2 < gout.g[2])
-          o = rank_lookup(ws.bitmap, ws.prefix, voxel_key(c.x, o0, o1, o2, gout), cap_coarse);
-      }
-    }
+    uint32_t cell;
+    if ((unsigned)c.x < (unsigned)gin.batch && tap_output_cell(c, k, gout, kr, &cell))
+      o = rank_lookup(ws.bitmap, ws.prefix, cell, cap_coarse);
     map[(size_t)k * cap + row] = o;
   }
 }
