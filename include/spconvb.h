@@ -202,6 +202,11 @@ typedef struct spconvb_conv_params {
   float mid_scale;
   int32_t res_relu;
   int32_t force_simt;     /* use the CUDA-core kernel (any channel count) */
+  int32_t wait_test;      /* 0 in normal use.  Self-test of the bounded waits of the tensor-core
+                           * kernel: w > 0 makes its producers withhold the "stage full" signal
+                           * from the w-th K chunk of every CTA on, so the consumer's wait must
+                           * run out; the launch then ends with SPCONVB_ST_TIMEOUT in the status
+                           * block, its output undefined, the context and TMEM usable */
 } spconvb_conv_params;
 
 /* Bytes of the packed device image of a weight tensor for the tensor-core path. */

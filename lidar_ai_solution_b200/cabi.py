@@ -27,7 +27,7 @@ class ConvParams(C.Structure):
         ("act", C.c_int32), ("out_kind", C.c_int32), ("inv_out_scale", C.c_float),
         ("res", C.c_void_p), ("res_kind", C.c_int32), ("res_scale", C.c_float),
         ("mid_kind", C.c_int32), ("mid_inv_scale", C.c_float), ("mid_scale", C.c_float),
-        ("res_relu", C.c_int32), ("force_simt", C.c_int32),
+        ("res_relu", C.c_int32), ("force_simt", C.c_int32), ("wait_test", C.c_int32),
     ]
 
 

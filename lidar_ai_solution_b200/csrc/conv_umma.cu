@@ -64,6 +64,7 @@ int conv_umma_launch(const spconvb_conv_params& p, const void* in, const int32_t
   a.out = (uint8_t*)out;
   a.status = status;
   a.kvol = p.kvol;
+  a.wait_test = p.wait_test;
   // Copies of the weights along the accumulator lanes, and residency.  Every copy lets
   // more epilogue warps share a tile, but a streamed stage always moves 128 weight rows,
   // as much L2 traffic as the gathered rows cost.  So: the most copies with which all

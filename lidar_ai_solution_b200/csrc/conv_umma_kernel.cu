@@ -309,7 +309,8 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
           cp_async_wait<kLag>();
           fence_proxy_async();  // generic-proxy writes -> async-proxy reads of the MMA
           __syncwarp();
-          if (lane == 0) mbar_arrive(bar_full + 8 * ((it - kLag) % kStages));
+          if (lane == 0 && !(a.wait_test > 0 && it - kLag + 1u >= (uint32_t)a.wait_test))
+            mbar_arrive(bar_full + 8 * ((it - kLag) % kStages));
         }
       }
     }
@@ -318,7 +319,9 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
     __syncwarp();
     if (alive && lane == 0) {
       const uint32_t first = it > (uint32_t)kLag ? it - kLag : 0u;
-      for (uint32_t i = first; i < it; ++i) mbar_arrive(bar_full + 8 * (i % kStages));
+      for (uint32_t i = first; i < it; ++i)
+        if (!(a.wait_test > 0 && i + 1u >= (uint32_t)a.wait_test))
+          mbar_arrive(bar_full + 8 * (i % kStages));
     }
   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------ MMA issue

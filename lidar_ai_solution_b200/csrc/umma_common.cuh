@@ -26,6 +26,7 @@ struct UmmaArgs {
   int kvol;
   int w_rep;       // copies of each weight chunk along the 128 accumulator lanes (1..128/Cout)
   int w_resident;  // 1: all chunks stay in shared memory for the whole launch; 0: streamed
+  int wait_test;   // > 0: producers withhold "stage full" from this chunk on (self-test)
   Epilogue ep;
 };
 

@@ -465,3 +465,31 @@ def test_inverse_map_is_the_strided_map_with_rows_swapped():
     inv = ops.inverse_map(dc, n_ptr, grid, ws, oc.shape[0], ks, st_, pd, status=st)
     torch.cuda.synchronize()
     assert np.array_equal(inv.cpu().numpy(), ref)
+
+
+def test_conv_bounded_wait_runs_out_and_the_context_survives():
+    """Failure detection without a GPU fault: with `wait_test` the producers of the
+    tensor-core kernel never signal a stage, so the MMA role's wait on it must run out
+    (250 ms), raise the CTA-wide abort flag, let every role leave its loop, free TMEM and
+    return with SPCONVB_ST_TIMEOUT in the status block.  The next launch on the same
+    context is then bit-exact again."""
+    ops = _ops()
+    from lidar_ai_solution_b200 import cabi
+    grid, n, c = (41, 180, 180), 2000, 32
+    pb = int8_problem(n, c, c, grid, seed=77)
+    m_ref, _ = orc.subm_map(pb["coords"], grid)
+    ref = orc.conv_i8(pb["xq"], m_ref, n, pb["wq"], pb["scale"], pb["bias"], orc.ACT_RELU,
+                      orc.KIND_I8, 9.0)
+    wts = ops.ConvWeights(pb["wq"], ops.I8, pb["scale"], pb["bias"])
+    x, m, n_ptr = _dev(pb["xq"]), _dev(m_ref), ops.device_count(n)
+    st = ops.new_status()
+    ops.conv_forward(x, m, n_ptr, wts, act=ops.ACT_RELU, out_kind=ops.I8, inv_out_scale=9.0,
+                     status=st, wait_test=1)
+    torch.cuda.synchronize()
+    assert int(st.cpu().numpy()[0]) & cabi.ST_TIMEOUT
+    st.zero_()
+    out = ops.conv_forward(x, m, n_ptr, wts, act=ops.ACT_RELU, out_kind=ops.I8,
+                           inv_out_scale=9.0, status=st)
+    torch.cuda.synchronize()
+    _status_ok(st)
+    assert np.array_equal(out.cpu().numpy(), ref)
