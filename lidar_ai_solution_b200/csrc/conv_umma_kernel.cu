@@ -58,14 +58,12 @@ namespace {
 
 constexpr int kTileRows = 256;  // most voxel rows per tile: the largest N of the MMA
 constexpr int kMmaM = 128;      // accumulator lanes: output channels, padded
-template <int COUT>
-struct Ring {
-  // as deep as shared memory allows next to the index staging area
-  static constexpr int kStages = 4;
-  // A producer signals a stage "full" kLag chunks after issuing its copies; the
-  // other kStages - kLag stages are slack for the round trip through the MMA.
-  static constexpr int kLag = 1;
-};
+// Stage ring: as deep as shared memory allows next to the index staging area (a stage is
+// 32 KB of rows + 16 KB of weights).  A producer signals a stage "full" kLag chunks after
+// issuing its copies; the other kStages - kLag stages are slack for the round trip
+// through the MMA.
+constexpr int kStages = 4;
+constexpr int kLag = 1;
 constexpr int kRowsBytes = kTileRows * kChunk;  // gathered rows of one stage
 constexpr int kEpiWarps = 8;
 constexpr int kMmaWarp = 8;
@@ -127,9 +125,8 @@ __device__ __forceinline__ void quad_transpose_h16(uint32_t& w0, uint32_t& w1, u
   if (hi) w0 = other; else w1 = other;
 }
 
-template <int COUT>
 constexpr size_t umma_smem_bytes() {
-  return 1024 + (size_t)Ring<COUT>::kStages * (kRowsBytes + kMmaM * kChunk) +
+  return 1024 + (size_t)kStages * (kRowsBytes + kMmaM * kChunk) +
          (size_t)kMaxTaps * kTileRows * sizeof(int32_t) + 256;
 }
 
@@ -138,8 +135,6 @@ template <bool INT8, int RB, int COUT>
 __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArgs a) {
   constexpr int kWBytes = kMmaM * kChunk;      // weight stage when streaming: 128 rows
   constexpr int kWChunk = COUT * kChunk;       // one copy of a chunk, as packed in global memory
-  constexpr int kStages = Ring<COUT>::kStages;
-  constexpr int kLag = Ring<COUT>::kLag;
   constexpr int OPC = RB <= kChunk ? kChunk / RB : 1;   // taps per chunk
   constexpr int SPO = RB <= kChunk ? RB / 16 : 8;       // 16-byte segments per tap per chunk
   constexpr int CPT = RB <= kChunk ? 1 : RB / kChunk;   // chunks per tap
@@ -567,7 +562,7 @@ int launch_one(const UmmaArgs& args, uint32_t launch_rows, cudaStream_t st) {
   static bool attr_done[64] = {};
   int dev = 0;
   SPCONVB_CUDA_TRY(cudaGetDevice(&dev));
-  constexpr size_t smem = umma_smem_bytes<COUT>();
+  constexpr size_t smem = umma_smem_bytes();
   if (dev < 0 || dev >= 64 || !attr_done[dev]) {
     SPCONVB_CUDA_TRY(cudaFuncSetAttribute(conv_umma_kernel<INT8, RB, COUT>,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize,

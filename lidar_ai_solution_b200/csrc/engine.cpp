@@ -43,11 +43,6 @@ static float half_bits_to_float(uint16_t h) {
   r.x = h;
   return __half2float(__half(r));
 }
-static uint16_t float_to_half_bits(float f) {
-  __half_raw r = __half_raw(__float2half_rn(f));
-  return r.x;
-}
-
 // ------------------------------------------------------------------ builder
 int Builder::new_tensor(const std::string& name, int producer) {
   GTensor t;
