@@ -493,3 +493,47 @@ def test_conv_bounded_wait_runs_out_and_the_context_survives():
     torch.cuda.synchronize()
     _status_ok(st)
     assert np.array_equal(out.cpu().numpy(), ref)
+
+
+def _shape_sweep_cases():
+    rng = np.random.default_rng(2024)
+    chans = [16, 32, 64, 128]
+    cases = []
+    for i in range(28):
+        cin, cout = int(rng.choice(chans)), int(rng.choice(chans))
+        n = int(rng.choice([1, 31, 33, 255, 257, 1000, 4736, 4737, 9473, 20000, 37889]))
+        kind = ["subm", "down", "k311"][i % 3]
+        cases.append((cin, cout, n, kind, i % 2 == 0, 100 + i))
+    return cases
+
+
+@pytest.mark.parametrize("cin,cout,n,kind,i8_out,seed", _shape_sweep_cases())
+def test_conv_int8_shape_sweep_bit_exact(cin, cout, n, kind, i8_out, seed):
+    """Channel pairs select how many copies of the weights sit on the accumulator lanes and
+    whether they stay resident; row counts select the tile height (32..256) and leave
+    partial tiles; the three rulebook kinds give 27 or 3 taps.  Everything int8, so the
+    tensor-core kernel must match the oracle bit for bit."""
+    ops = _ops()
+    grid = (41, 180, 180)
+    kvol = 3 if kind == "k311" else 27
+    pb = int8_problem(n, cin, cout, grid, seed=seed, kvol=kvol)
+    if kind == "subm":
+        m_ref, _ = orc.subm_map(pb["coords"], grid)
+        n_out = n
+    elif kind == "down":
+        _, m_ref, _, _, n_out = orc.down_map(pb["coords"], grid, (3, 3, 3), (2, 2, 2), (1, 1, 1))
+    else:
+        _, m_ref, _, _, n_out = orc.down_map(pb["coords"], grid, (3, 1, 1), (2, 1, 1), (0, 0, 0))
+    okind = orc.KIND_I8 if i8_out else orc.KIND_F16
+    inv = 11.0 if i8_out else 1.0
+    ref = orc.conv_i8(pb["xq"], m_ref, n_out, pb["wq"], pb["scale"], pb["bias"], orc.ACT_RELU,
+                      okind, inv)
+    wts = ops.ConvWeights(pb["wq"], ops.I8, pb["scale"], pb["bias"])
+    assert wts.packed is not None
+    st = ops.new_status()
+    md = _dev(np.ascontiguousarray(m_ref))
+    out = ops.conv_forward(_dev(pb["xq"]), md, ops.device_count(n_out), wts, act=ops.ACT_RELU,
+                           out_kind=ops.I8 if i8_out else ops.F16, inv_out_scale=inv, status=st)
+    torch.cuda.synchronize()
+    _status_ok(st)
+    assert np.array_equal(out.cpu().numpy()[:n_out].view(np.uint8), ref[:n_out].view(np.uint8))
