@@ -121,10 +121,26 @@ WORKLOADS = {
     "centerpoint_int8_mixed": dict(
         kind="centerpoint", precision="int8", voxels=(60000, 200000), bound=520000,
         name="centerpoint_scn_int8 full backbone, 41x1440x1440 grid, voxel counts U[60k,200k]"),
+    "centerpoint_int8_fixture": dict(
+        kind="centerpoint", precision="int8", voxels=(79745, 79745), bound=OUTPUT_BOUND,
+        fixture="centerpoint_zyx",
+        name="centerpoint_scn_int8 full backbone, the reference's 79 745-voxel sample frame "
+             "(coordinates from tests/golden/fixture_coords.npz, synthetic features)"),
     "bevfusion_fp16": dict(
         kind="bevfusion", precision="fp16", voxels=(VOXELS, VOXELS), bound=OUTPUT_BOUND,
         name="bevfusion lidar SparseEncoder fp16, 41x1440x1440 grid, ~120k active voxels/frame"),
 }
+
+
+def workload_frame(spec, seed):
+    """(features, coords) of one frame of a workload."""
+    if "fixture" in spec:
+        from lidar_ai_solution_b200 import scenes
+        zyx = np.load(os.path.join(ROOT, "tests", "golden", "fixture_coords.npz"))[spec["fixture"]]
+        coords = np.zeros((len(zyx), 4), np.int32)
+        coords[:, 1:] = zyx
+        return scenes.make_point_features(coords, seed), coords
+    return make_frames(1, seed, frame_voxels(spec, seed))[0]
 
 
 def frame_voxels(spec, seed):
@@ -198,7 +214,7 @@ def run_reference(args, rank, world):
         qm = models.quantize(qm, ranges)
     steps = max(1, min(args.steps, 6))
     warm = max(0, min(args.warmup, 1))
-    frames = [make_frames(1, s, frame_voxels(spec, s))[0] for s in range(1, 1 + steps + warm)]
+    frames = [workload_frame(spec, s) for s in range(1, 1 + steps + warm)]
     for f, c in frames[:warm]:
         graph_oracle.run(qm, f, c, GRID, spec["precision"])
     t0 = time.perf_counter()
@@ -246,7 +262,7 @@ def run_gpu(args, rank, world, local_rank):
     onnx_writer.save(qm, onnx_path)
 
     F, R = args.frames, max(1, min(args.replicas, args.frames))
-    frames = [make_frames(1, s, frame_voxels(spec, s))[0] for s in sharding.frame_seeds(rank, F)]
+    frames = [workload_frame(spec, s) for s in sharding.frame_seeds(rank, F)]
     streams = [torch.cuda.Stream(device=dev) for _ in range(R)]
     engines = [engine.Engine.from_onnx(onnx_path, precision, 0, 0, dev) for _ in range(R)]
     for e in engines:
