@@ -245,6 +245,13 @@ SPCONVB_API int spconvb_add(const void* a, int32_t a_kind, float a_scale, const 
 SPCONVB_API int spconvb_relu(const void* x, int32_t kind, int32_t channels, const uint32_t* n_ptr,
                              uint32_t launch_rows, void* out, void* stream);
 
+/* Folds max |x| over rows [0, min(*n_ptr, launch_rows)) x channels into *out (a float in
+ * device memory that the caller zeroed before the first call; calls accumulate).  int8
+ * tensors count in quantised units.  This is the statistic of plain absmax calibration. */
+SPCONVB_API int spconvb_absmax(const void* x, int32_t kind, int32_t channels,
+                               const uint32_t* n_ptr, uint32_t launch_rows, float* out,
+                               void* stream);
+
 /* Copy rows [*n_ptr][cin] to [*n_ptr][cout_pad] with zero padding and an
  * optional precision change (fp16 -> int8 with inv_scale, int8 -> fp16 with scale). */
 SPCONVB_API int spconvb_convert(const void* x, int32_t in_kind, int32_t cin, int32_t out_kind,
@@ -472,6 +479,28 @@ SPCONVB_API int spconvb_engine_last_launches(const spconvb_engine* e);
  * reported by spconvb_engine_describe: a '\n' separated text table, one line
  * per executed step: "kind name rows_ptr_index cin cout kvol in_bytes out_bytes". */
 SPCONVB_API const char* spconvb_engine_describe(const spconvb_engine* e);
+
+/* Run-time precision control of the v1.0 interface
+ * (CUDA-CenterPoint/3rdparty/libspconv/include/spconv/engine.hpp:81-91).  The engine keeps
+ * the graph it was built from; these calls edit it and spconvb_engine_reconfigure rebuilds
+ * the executable engine from it (weights are re-quantised and re-packed, buffers are
+ * re-planned at the next forward; outputs of earlier forwards become invalid).
+ *
+ * set_node_precision: `key` is a node name (by_optype = 0) or an operator type
+ * ("SparseConvolution", "Add", "Relu", "ScatterDense"; by_optype = 1); returns the number of
+ * nodes changed or a negative error.  Takes effect at the next reconfigure.
+ *
+ * set_int8_calibration(1) + reconfigure: the engine runs in fp16 and every forward folds
+ * the absmax of every tensor into a running maximum.  set_int8_calibration(0): the maxima
+ * become the dynamic ranges of the graph (conv: its input's range and per-output-channel
+ * weight ranges; Add: the larger of its operands' for both), every node not touched by
+ * set_node_precision is set to int8, and the engine's main precision becomes int8; the next
+ * reconfigure builds that engine. */
+SPCONVB_API int spconvb_engine_set_node_precision(spconvb_engine* e, const char* key,
+                                                  int32_t by_optype, int32_t compute_precision,
+                                                  int32_t output_precision);
+SPCONVB_API int spconvb_engine_set_int8_calibration(spconvb_engine* e, int32_t enable);
+SPCONVB_API int spconvb_engine_reconfigure(spconvb_engine* e, void* stream);
 
 /* Logging (spconv::set_logger_level, engine.hpp:171): 0 verbose, 1 warn, 2 error, 99 quiet. */
 SPCONVB_API void spconvb_set_log_level(int32_t level);

@@ -70,6 +70,7 @@ SYMBOLS = {
     "spconvb_add": (C.c_int, [_VP, C.c_int32, C.c_float, _VP, C.c_int32, C.c_float, C.c_int32,
                               _VP, C.c_uint32, C.c_int32, C.c_int32, C.c_float, _VP, _VP]),
     "spconvb_relu": (C.c_int, [_VP, C.c_int32, C.c_int32, _VP, C.c_uint32, _VP, _VP]),
+    "spconvb_absmax": (C.c_int, [_VP, C.c_int32, C.c_int32, _VP, C.c_uint32, _VP, _VP]),
     "spconvb_convert": (C.c_int, [_VP, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_float,
                                   _VP, C.c_uint32, _VP, _VP]),
     "spconvb_scatter_dense": (C.c_int, [_VP, C.c_int32, C.c_float, _VP, _VP, C.c_uint32,

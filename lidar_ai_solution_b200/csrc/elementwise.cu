@@ -107,6 +107,23 @@ __global__ void relu_kernel(const void* x, int kind, int channels, const uint32_
   }
 }
 
+// max |x| over the first *n_ptr rows, folded into *out with an integer atomicMax (the bit
+// patterns of non-negative floats order like the values).  NaN elements are skipped.
+__global__ void absmax_kernel(const void* x, int kind, int channels, const uint32_t* n_ptr,
+                              uint32_t cap, float* out) {
+  const size_t total = (size_t)min(*n_ptr, cap) * channels;
+  float m = 0.f;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (size_t)gridDim.x * blockDim.x) {
+    const float v = kind == SPCONVB_I8 ? fabsf((float)((const int8_t*)x)[i])
+                                       : fabsf(__half2float(((const __half*)x)[i]));
+    if (v == v) m = fmaxf(m, v);
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+  if ((threadIdx.x & 31) == 0 && m > 0.f) atomicMax((int*)out, __float_as_int(m));
+}
+
 __global__ void convert_kernel(const void* x, int in_kind, int cin, int out_kind, int cout,
                                float s, const uint32_t* n_ptr, void* out) {
   const size_t total = (size_t)(*n_ptr) * cout;
@@ -223,6 +240,16 @@ int spconvb_relu(const void* x, int32_t kind, int32_t channels, const uint32_t* 
   const uint32_t work = clamp_u32((size_t)launch_rows * channels);
   relu_kernel<<<blocks_for(work, 256), 256, 0, (cudaStream_t)stream>>>(x, kind, channels, n_ptr,
                                                                        out);
+  SPCONVB_LAUNCH_CHECK();
+  return SPCONVB_OK;
+}
+
+int spconvb_absmax(const void* x, int32_t kind, int32_t channels, const uint32_t* n_ptr,
+                   uint32_t launch_rows, float* out, void* stream) {
+  if (!x || !out || !n_ptr || channels < 1 || launch_rows < 1) return SPCONVB_E_ARG;
+  const uint32_t work = clamp_u32((size_t)launch_rows * channels);
+  absmax_kernel<<<blocks_for(work, 256), 256, 0, (cudaStream_t)stream>>>(x, kind, channels, n_ptr,
+                                                                         launch_rows, out);
   SPCONVB_LAUNCH_CHECK();
   return SPCONVB_OK;
 }

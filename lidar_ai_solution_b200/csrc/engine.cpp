@@ -643,6 +643,22 @@ int Engine::compile(const Builder& b, int precision, uint32_t build_flags, cudaS
   return SPCONVB_OK;
 }
 
+int Engine::collect_absmax(float* out, cudaStream_t st) {
+  if (!prepared_ || !out || !last_in_n_) return SPCONVB_E_ARG;
+  for (int r = 0; r < (int)rt.size(); ++r) {
+    const RTensor& t = rt[r];
+    if (t.dense || t.alias_of >= 0 || !t.data || t.cs < 0) continue;
+    const CoordSet& cs = coordsets[t.cs];
+    const bool ext = cs.external;
+    const int ch = r == input_rt_ ? input_channels_ : t.channels;
+    if (ch < 1) continue;
+    const int rc = spconvb_absmax(t.data, t.kind, ch, ext ? last_in_n_ : cs.n_ptr,
+                                  ext ? last_in_cap_ : cs.cap, out + r, st);
+    if (rc != SPCONVB_OK) return rc;
+  }
+  return SPCONVB_OK;
+}
+
 static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
 int Engine::prepare(const int32_t grid[3], int batch) {
@@ -784,6 +800,8 @@ int Engine::forward(const void* features, const int32_t* indices, uint32_t cap_r
     in_n = slot;
   }
   rt[input_rt_].data = const_cast<void*>(features);
+  last_in_n_ = in_n;
+  last_in_cap_ = in_cap;
 
   auto cs_coords = [&](int c) { return coordsets[c].external ? indices : coordsets[c].coords; };
   auto cs_n = [&](int c) { return coordsets[c].external ? in_n : coordsets[c].n_ptr; };

@@ -145,6 +145,10 @@ class Engine {
               const uint32_t* n_dev, const int32_t grid[3], int batch, cudaStream_t st,
               const Profile* prof = nullptr);
 
+  // Folds max |x| of every sparse runtime tensor of the last forward into out[r] (device
+  // floats, one per runtime tensor), on the stream of that forward.
+  int collect_absmax(float* out, cudaStream_t st);
+
   std::vector<CoordSet> coordsets;
   std::vector<Rule> rules;
   std::vector<RTensor> rt;
@@ -160,6 +164,8 @@ class Engine {
  private:
   int input_rt_ = -1;
   int input_channels_ = 0;
+  const uint32_t* last_in_n_ = nullptr;  // row count of the caller's rows in the last forward
+  uint32_t last_in_cap_ = 0;
   bool prepared_ = false;
   int32_t grid_[3] = {0, 0, 0};
   int batch_ = 0;

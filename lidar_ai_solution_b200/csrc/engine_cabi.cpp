@@ -2,7 +2,12 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <cuda_fp16.h>
+#include <math.h>
+
+#include <memory>
 #include <string>
+#include <vector>
 
 #include "engine.hpp"
 
@@ -12,7 +17,17 @@ struct spconvb_builder {
   Builder b;
 };
 struct spconvb_engine {
-  Engine e;
+  std::unique_ptr<Engine> e;   // the executable engine, rebuilt by reconfigure
+  Builder graph;               // what it was built from, edited by the precision setters
+  int32_t precision = SPCONVB_PRECISION_FP16;
+  uint32_t flags = 0;
+  std::vector<char> user_prec;   // per node: precision set explicitly by the caller
+  bool want_calibration = false; // state asked for; applied by the next reconfigure
+  bool collecting = false;       // the live engine is the fp16 calibration engine
+  float* absmax = nullptr;       // device, one per runtime tensor of the calibration engine
+  ~spconvb_engine() {
+    if (absmax) cudaFree(absmax);
+  }
 };
 
 namespace {
@@ -163,7 +178,15 @@ spconvb_engine* spconvb_builder_build(spconvb_builder* b, int32_t precision, uin
   spconvb_engine* e = nullptr;
   if (b) {
     e = new (std::nothrow) spconvb_engine();
-    rc = e ? e->e.compile(b->b, precision, flags, (cudaStream_t)stream) : SPCONVB_E_NOMEM;
+    if (e) {
+      e->e.reset(new (std::nothrow) Engine());
+      e->graph = b->b;
+      e->precision = precision;
+      e->flags = flags;
+      e->user_prec.assign(b->b.nodes.size(), 0);
+    }
+    rc = e && e->e ? e->e->compile(e->graph, precision, flags, (cudaStream_t)stream)
+                   : SPCONVB_E_NOMEM;
     if (rc != SPCONVB_OK) {
       delete e;
       e = nullptr;
@@ -230,35 +253,140 @@ int spconvb_onnx_inspect(const char* path, char* buf, size_t buf_bytes) {
   return SPCONVB_OK;
 }
 
+int spconvb_engine_set_node_precision(spconvb_engine* e, const char* key, int32_t by_optype,
+                                      int32_t compute_precision, int32_t output_precision) {
+  if (!e || !key) return SPCONVB_E_ARG;
+  auto ok = [](int32_t p) { return p == SPCONVB_PRECISION_FP16 || p == SPCONVB_PRECISION_INT8; };
+  if (!ok(compute_precision) || !ok(output_precision)) return SPCONVB_E_ARG;
+  static const struct { const char* name; OpKind op; } kinds[] = {
+      {"SparseConvolution", OP_CONV}, {"Add", OP_ADD}, {"QuantAdd", OP_ADD}, {"Relu", OP_RELU},
+      {"ScatterDense", OP_DENSE}};
+  int changed = 0;
+  for (size_t i = 0; i < e->graph.nodes.size(); ++i) {
+    GNode& n = e->graph.nodes[i];
+    bool hit = false;
+    if (by_optype) {
+      for (const auto& k : kinds) hit = hit || (n.op == k.op && strcmp(key, k.name) == 0);
+    } else {
+      hit = n.name == key;
+    }
+    if (!hit) continue;
+    n.prec = compute_precision;
+    n.out_prec = output_precision;
+    e->user_prec[i] = 1;
+    ++changed;
+  }
+  return changed;
+}
+
+int spconvb_engine_set_int8_calibration(spconvb_engine* e, int32_t enable) {
+  if (!e) return SPCONVB_E_ARG;
+  if (enable) {
+    e->want_calibration = true;
+    return SPCONVB_OK;
+  }
+  e->want_calibration = false;
+  if (!e->collecting) return SPCONVB_OK;
+  // the running maxima become the dynamic ranges of the graph
+  if (cudaDeviceSynchronize() != cudaSuccess) return SPCONVB_E_DEVICE;
+  std::vector<float> host(e->e->rt.size(), 0.f);
+  if (cudaMemcpy(host.data(), e->absmax, sizeof(float) * host.size(), cudaMemcpyDeviceToHost) !=
+      cudaSuccess)
+    return SPCONVB_E_DEVICE;
+  auto range_of = [&](int graph_tensor) -> float {
+    if (!e->graph.valid_tensor(graph_tensor)) return 1e-6f;
+    auto it = e->e->by_name.find(e->graph.tensors[graph_tensor].name);
+    const float v = it == e->e->by_name.end() ? 0.f : host[it->second];
+    return v > 1e-6f ? v : 1e-6f;
+  };
+  for (size_t i = 0; i < e->graph.nodes.size(); ++i) {
+    GNode& n = e->graph.nodes[i];
+    if (n.op == OP_CONV) {
+      n.in_dr = range_of(n.in0);
+      const size_t per_out = n.cout > 0 ? n.weight.size() / (size_t)n.cout : 0;
+      n.wdr.assign(n.cout, 0.f);
+      for (int c = 0; c < n.cout; ++c) {
+        float m = 0.f;
+        for (size_t j = 0; j < per_out; ++j) {
+          __half_raw r;
+          r.x = n.weight[(size_t)c * per_out + j];
+          m = fmaxf(m, fabsf(__half2float(__half(r))));
+        }
+        n.wdr[c] = m;
+      }
+    } else if (n.op == OP_ADD) {
+      n.a_dr = n.b_dr = fmaxf(range_of(n.in0), range_of(n.in1));
+    } else {
+      continue;
+    }
+    if (!e->user_prec[i]) n.prec = n.out_prec = SPCONVB_PRECISION_INT8;
+  }
+  e->precision = SPCONVB_PRECISION_INT8;
+  e->collecting = false;  // the fp16 engine keeps running until the next reconfigure
+  return SPCONVB_OK;
+}
+
+int spconvb_engine_reconfigure(spconvb_engine* e, void* stream) {
+  if (!e) return SPCONVB_E_ARG;
+  if (cudaDeviceSynchronize() != cudaSuccess) return SPCONVB_E_DEVICE;
+  const bool calib = e->want_calibration;
+  std::unique_ptr<Engine> fresh(new (std::nothrow) Engine());
+  if (!fresh) return SPCONVB_E_NOMEM;
+  const int rc = fresh->compile(
+      e->graph, calib ? SPCONVB_PRECISION_FP16 : e->precision,
+      calib ? (SPCONVB_BUILD_KEEP_TENSORS | SPCONVB_BUILD_NO_FUSION) : e->flags,
+      (cudaStream_t)stream);
+  if (rc != SPCONVB_OK) return rc;
+  if (e->absmax) {
+    cudaFree(e->absmax);
+    e->absmax = nullptr;
+  }
+  if (calib) {
+    const size_t bytes = sizeof(float) * (fresh->rt.size() + 1);
+    if (cudaMalloc((void**)&e->absmax, bytes) != cudaSuccess) return SPCONVB_E_NOMEM;
+    cudaMemset(e->absmax, 0, bytes);
+  }
+  e->e = std::move(fresh);
+  e->collecting = calib;
+  return SPCONVB_OK;
+}
+
 void spconvb_engine_destroy(spconvb_engine* e) { delete e; }
 
 int spconvb_engine_forward(spconvb_engine* e, const void* features, uint32_t n,
                            const int32_t* indices, const int32_t grid[3], int32_t batch,
                            void* stream) {
   if (!e) return SPCONVB_E_ARG;
-  return e->e.forward(features, indices, n, n, nullptr, grid, batch, (cudaStream_t)stream);
+  int rc = e->e->forward(features, indices, n, n, nullptr, grid, batch, (cudaStream_t)stream);
+  if (rc == SPCONVB_OK && e->collecting)
+    rc = e->e->collect_absmax(e->absmax, (cudaStream_t)stream);
+  return rc;
 }
 
 int spconvb_engine_forward_dds(spconvb_engine* e, const void* features, const int32_t* indices,
                                uint32_t cap_rows, const uint32_t* n_dev, const int32_t grid[3],
                                int32_t batch, void* stream) {
   if (!e || !n_dev) return SPCONVB_E_ARG;
-  return e->e.forward(features, indices, cap_rows, 0, n_dev, grid, batch, (cudaStream_t)stream);
+  int rc = e->e->forward(features, indices, cap_rows, 0, n_dev, grid, batch,
+                         (cudaStream_t)stream);
+  if (rc == SPCONVB_OK && e->collecting)
+    rc = e->e->collect_absmax(e->absmax, (cudaStream_t)stream);
+  return rc;
 }
 
 int spconvb_engine_prepare(spconvb_engine* e, const int32_t grid[3], int32_t batch) {
   if (!e || !grid) return SPCONVB_E_ARG;
-  return e->e.prepare(grid, batch);
+  return e->e->prepare(grid, batch);
 }
 
 int spconvb_engine_num_outputs(const spconvb_engine* e) {
-  return e ? (int)e->e.outputs.size() : SPCONVB_E_ARG;
+  return e ? (int)e->e->outputs.size() : SPCONVB_E_ARG;
 }
 
 int spconvb_engine_output(const spconvb_engine* e, int i, void** data, int64_t shape[8],
                           int32_t* ndim, int32_t* kind, int32_t* dense) {
-  if (!e || i < 0 || i >= (int)e->e.outputs.size()) return SPCONVB_E_ARG;
-  const RTensor& t = e->e.rt[e->e.outputs[i]];
+  if (!e || i < 0 || i >= (int)e->e->outputs.size()) return SPCONVB_E_ARG;
+  const RTensor& t = e->e->rt[e->e->outputs[i]];
   if (data) *data = t.data;
   if (kind) *kind = t.kind;
   if (dense) *dense = t.dense ? 1 : 0;
@@ -267,7 +395,7 @@ int spconvb_engine_output(const spconvb_engine* e, int i, void** data, int64_t s
     for (auto v : t.shape)
       if (nd < 8 && shape) shape[nd++] = v;
   } else if (shape) {
-    shape[0] = t.cs >= 0 ? e->e.coordsets[t.cs].cap : 0;
+    shape[0] = t.cs >= 0 ? e->e->coordsets[t.cs].cap : 0;
     shape[1] = t.channels;
     nd = 2;
   }
@@ -277,9 +405,9 @@ int spconvb_engine_output(const spconvb_engine* e, int i, void** data, int64_t s
 
 int spconvb_engine_tensor(const spconvb_engine* e, const char* name, spconvb_tensor_view* v) {
   if (!e || !name || !v) return SPCONVB_E_ARG;
-  auto it = e->e.by_name.find(name);
-  if (it == e->e.by_name.end()) return SPCONVB_E_ARG;
-  const RTensor& t = e->e.rt[it->second];
+  auto it = e->e->by_name.find(name);
+  if (it == e->e->by_name.end()) return SPCONVB_E_ARG;
+  const RTensor& t = e->e->rt[it->second];
   memset(v, 0, sizeof(*v));
   v->features = t.data;
   v->kind = t.kind;
@@ -287,7 +415,7 @@ int spconvb_engine_tensor(const spconvb_engine* e, const char* name, spconvb_ten
   v->scale = t.kind == SPCONVB_I8 ? t.dr / 127.0f : 1.f;
   v->dense = t.dense ? 1 : 0;
   if (t.cs >= 0) {
-    const CoordSet& cs = e->e.coordsets[t.cs];
+    const CoordSet& cs = e->e->coordsets[t.cs];
     v->coords = cs.coords;
     v->n_ptr = cs.n_ptr;
     v->cap = cs.cap;
@@ -297,14 +425,14 @@ int spconvb_engine_tensor(const spconvb_engine* e, const char* name, spconvb_ten
 }
 
 const char* spconvb_engine_tensor_names(const spconvb_engine* e) {
-  return e ? e->e.names_text.c_str() : "";
+  return e ? e->e->names_text.c_str() : "";
 }
 
 const char* spconvb_engine_describe(const spconvb_engine* e) {
-  return e ? e->e.describe_text.c_str() : "";
+  return e ? e->e->describe_text.c_str() : "";
 }
 
-int spconvb_engine_num_steps(const spconvb_engine* e) { return e ? (int)e->e.steps.size() : 0; }
+int spconvb_engine_num_steps(const spconvb_engine* e) { return e ? (int)e->e->steps.size() : 0; }
 
 int spconvb_engine_profile(spconvb_engine* e, const void* features, uint32_t n,
                            const int32_t* indices, const int32_t grid[3], int32_t batch,
@@ -317,13 +445,13 @@ int spconvb_engine_profile(spconvb_engine* e, const void* features, uint32_t n,
   p.reps = reps < 1 ? 1 : reps;
   p.flush = flush;
   p.flush_bytes = flush_bytes;
-  return e->e.forward(features, indices, n, n, nullptr, grid, batch, (cudaStream_t)stream, &p);
+  return e->e->forward(features, indices, n, n, nullptr, grid, batch, (cudaStream_t)stream, &p);
 }
 
 int spconvb_engine_coordset(const spconvb_engine* e, int i, uint32_t** n_ptr, uint32_t* cap,
                             int32_t grid[3]) {
-  if (!e || i < 0 || i >= (int)e->e.coordsets.size()) return SPCONVB_E_ARG;
-  const CoordSet& cs = e->e.coordsets[i];
+  if (!e || i < 0 || i >= (int)e->e->coordsets.size()) return SPCONVB_E_ARG;
+  const CoordSet& cs = e->e->coordsets[i];
   if (n_ptr) *n_ptr = cs.n_ptr;
   if (cap) *cap = cs.cap;
   if (grid)
@@ -331,17 +459,17 @@ int spconvb_engine_coordset(const spconvb_engine* e, int i, uint32_t** n_ptr, ui
   return SPCONVB_OK;
 }
 
-int spconvb_engine_num_rules(const spconvb_engine* e) { return e ? (int)e->e.rules.size() : 0; }
+int spconvb_engine_num_rules(const spconvb_engine* e) { return e ? (int)e->e->rules.size() : 0; }
 
 int spconvb_engine_rule(const spconvb_engine* e, int i, int32_t** map, uint32_t* cap,
                         int32_t* kvol, uint32_t** n_out_ptr, uint32_t** n_in_ptr) {
-  if (!e || i < 0 || i >= (int)e->e.rules.size()) return SPCONVB_E_ARG;
-  const Rule& r = e->e.rules[i];
+  if (!e || i < 0 || i >= (int)e->e->rules.size()) return SPCONVB_E_ARG;
+  const Rule& r = e->e->rules[i];
   if (map) *map = r.map;
-  if (cap) *cap = e->e.coordsets[r.out_cs].cap;
+  if (cap) *cap = e->e->coordsets[r.out_cs].cap;
   if (kvol) *kvol = r.kvol;
-  if (n_out_ptr) *n_out_ptr = e->e.coordsets[r.out_cs].n_ptr;
-  if (n_in_ptr) *n_in_ptr = e->e.coordsets[r.in_cs].n_ptr;
+  if (n_out_ptr) *n_out_ptr = e->e->coordsets[r.out_cs].n_ptr;
+  if (n_in_ptr) *n_in_ptr = e->e->coordsets[r.in_cs].n_ptr;
   return SPCONVB_OK;
 }
 
@@ -364,13 +492,13 @@ int spconvb_copy_async(void* dst, const void* src, size_t bytes, int32_t directi
 
 int spconvb_engine_status(const spconvb_engine* e, uint32_t out[4], void* stream) {
   if (!e || !out) return SPCONVB_E_ARG;
-  if (!e->e.status) {
+  if (!e->e->status) {
     memset(out, 0, 4 * sizeof(uint32_t));
     return SPCONVB_OK;
   }
-  return spconvb_read_device(e->e.status, out, 4 * sizeof(uint32_t), stream);
+  return spconvb_read_device(e->e->status, out, 4 * sizeof(uint32_t), stream);
 }
 
-int spconvb_engine_last_launches(const spconvb_engine* e) { return e ? e->e.last_launches : 0; }
+int spconvb_engine_last_launches(const spconvb_engine* e) { return e ? e->e->last_launches : 0; }
 
 }  // extern "C"

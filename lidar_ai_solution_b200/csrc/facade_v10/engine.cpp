@@ -28,9 +28,8 @@ class ResultTensor : public DTensor {
   int dev = 0;
 };
 
-void warn_unsupported(const char* what) {
-  fprintf(stderr, "[spconv warn] %s is not implemented in this library; precisions and dynamic ranges "
-                  "come from the model file\n", what);
+int to_c(spconv::Precision p) {
+  return p == spconv::Precision::Int8 ? SPCONVB_PRECISION_INT8 : SPCONVB_PRECISION_FP16;
 }
 
 class EngineImpl : public Engine {
@@ -64,13 +63,27 @@ class EngineImpl : public Engine {
     return &result_;
   }
 
-  void reconfigure() override { warn_unsupported("reconfigure"); }
-  void set_int8_calibration(bool) override { warn_unsupported("set_int8_calibration"); }
-  void set_node_precision_byname(const char*, Precision, Precision) override {
-    warn_unsupported("set_node_precision_byname");
+  void reconfigure() override {
+    const int rc = spconvb_engine_reconfigure(e_, nullptr);
+    if (rc != SPCONVB_OK) fprintf(stderr, "[spconv] reconfigure failed: %s\n", spconvb_error_string(rc));
   }
-  void set_node_precision_byoptype(const char*, Precision, Precision) override {
-    warn_unsupported("set_node_precision_byoptype");
+  void set_int8_calibration(bool enable) override {
+    const int rc = spconvb_engine_set_int8_calibration(e_, enable ? 1 : 0);
+    if (rc != SPCONVB_OK)
+      fprintf(stderr, "[spconv] set_int8_calibration failed: %s\n", spconvb_error_string(rc));
+  }
+  void set_node_precision_byname(const char* name, Precision compute_precision,
+                                 Precision output_precision) override {
+    if (spconvb_engine_set_node_precision(e_, name, 0, to_c(compute_precision),
+                                          to_c(output_precision)) <= 0)
+      fprintf(stderr, "[spconv] set_node_precision_byname: no node named '%s'\n", name ? name : "");
+  }
+  void set_node_precision_byoptype(const char* optype, Precision compute_precision,
+                                   Precision output_precision) override {
+    if (spconvb_engine_set_node_precision(e_, optype, 1, to_c(compute_precision),
+                                          to_c(output_precision)) <= 0)
+      fprintf(stderr, "[spconv] set_node_precision_byoptype: no node of type '%s'\n",
+              optype ? optype : "");
   }
 
  private:

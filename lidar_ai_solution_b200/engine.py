@@ -183,6 +183,28 @@ class Engine:
     def last_launches(self):
         return int(self._lib.spconvb_engine_last_launches(self._h))
 
+    # -- run-time precision control (the v1.0 interface's setters) -----------------
+    def set_node_precision(self, key, compute_precision, output_precision, by_optype=False):
+        """Precision of the node called ``key`` (or of every node of operator type ``key``);
+        returns how many nodes changed.  Takes effect at the next ``reconfigure``."""
+        n = self._lib.spconvb_engine_set_node_precision(self._h, key.encode(), int(by_optype),
+                                                        compute_precision, output_precision)
+        if n < 0:
+            cabi.check(n, "set_node_precision")
+        return n
+
+    def set_int8_calibration(self, enable):
+        """True (+ ``reconfigure``): run in fp16 and collect every tensor's absmax over the
+        forwards that follow.  False: turn the maxima into the graph's dynamic ranges and
+        make int8 the main precision (+ ``reconfigure`` to build that engine)."""
+        cabi.check(self._lib.spconvb_engine_set_int8_calibration(self._h, int(bool(enable))),
+                   "set_int8_calibration")
+
+    def reconfigure(self, stream=None):
+        with torch.cuda.device(self.device):
+            cabi.check(self._lib.spconvb_engine_reconfigure(self._h, _stream_ptr(stream)),
+                       "reconfigure")
+
 
 def calibrate(model: dict, features, indices, grid) -> dict:
     """Plain absmax calibration on one frame: runs the model in fp16 on the GPU

@@ -64,6 +64,10 @@ SYMBOLS = {
     "spconvb_copy_async": (C.c_int, [_VP, _VP, C.c_size_t, C.c_int32, _VP]),
     "spconvb_engine_status": (C.c_int, [_VP, C.POINTER(C.c_uint32), _VP]),
     "spconvb_engine_last_launches": (C.c_int, [_VP]),
+    "spconvb_engine_set_node_precision": (C.c_int, [_VP, C.c_char_p, C.c_int32, C.c_int32,
+                                                    C.c_int32]),
+    "spconvb_engine_set_int8_calibration": (C.c_int, [_VP, C.c_int32]),
+    "spconvb_engine_reconfigure": (C.c_int, [_VP, _VP]),
     "spconvb_set_log_level": (None, [C.c_int32]),
     "spconvb_set_log_callback": (None, [LOG_FN]),
 }

@@ -443,3 +443,74 @@ def test_inverse_conv_needs_its_rulebook():
     [nd for nd in bad["nodes"] if nd.get("inverse")][0]["rulebook"] = "nowhere"
     with pytest.raises(RuntimeError):
         eng.Engine.from_model(bad, eng.PRECISION_FP16, 0)
+
+
+# ------------------------------------------ run-time calibration and precision setters
+def test_runtime_calibration_matches_offline_quantisation():
+    """The v1.0 interface's set_int8_calibration / set_node_precision_byname / reconfigure
+    (CUDA-CenterPoint/3rdparty/libspconv/include/spconv/engine.hpp:81-91) through the C ABI:
+    calibrating on one frame inside the engine and naming the exporter's fp16 layers gives
+    the same int8 engine, bit for bit, as quantising the model offline with the same
+    absmax ranges."""
+    eng = _engine_mod()
+    feats, coords = _frame(9000, seed=5)
+    model = _small_model("centerpoint", seed=4)
+    qm = models.quantize(model, eng.calibrate(model, _dev(feats), _dev(coords), GRID))
+    ref_e = eng.Engine.from_model(qm, eng.PRECISION_INT8, 0)
+    ref_e.forward(_dev(feats), _dev(coords), GRID)
+    torch.cuda.synchronize()
+    ref = ref_e.output(0).cpu().numpy()
+
+    e = eng.Engine.from_model(model, eng.PRECISION_FP16, 0)
+    e.forward(_dev(feats), _dev(coords), GRID)
+    torch.cuda.synchronize()
+    fp16_out = e.output(0).cpu().numpy()
+    e.set_int8_calibration(True)
+    e.reconfigure()
+    e.forward(_dev(feats), _dev(coords), GRID)
+    torch.cuda.synchronize()
+    assert np.array_equal(e.output(0).cpu().numpy().view(np.uint16), fp16_out.view(np.uint16))
+    e.set_int8_calibration(False)
+    nodes, roles = model["nodes"], model["roles"]
+    F16, I8 = eng.PRECISION_FP16, eng.PRECISION_INT8
+    assert e.set_node_precision(nodes[roles["conv_input"][0]]["name"], F16, F16) == 1
+    for i in roles["block0"]:
+        if nodes[i]["op"] == "conv":
+            assert e.set_node_precision(nodes[i]["name"], F16, F16) == 1
+        elif nodes[i]["op"] == "add":
+            assert e.set_node_precision(nodes[i]["name"], F16, I8) == 1
+    assert e.set_node_precision(nodes[roles["extra"][0]]["name"], I8, F16) == 1
+    assert e.set_node_precision("no such node", I8, I8) == 0
+    e.reconfigure()
+    e.forward(_dev(feats), _dev(coords), GRID)
+    torch.cuda.synchronize()
+    assert e.status()[0] == 0
+    got = e.output(0).cpu().numpy()
+    assert np.array_equal(got.view(np.uint16), ref.view(np.uint16))
+    assert not np.array_equal(got.view(np.uint16), fp16_out.view(np.uint16))
+
+
+def test_set_node_precision_by_optype_rebuilds_the_engine():
+    eng = _engine_mod()
+    feats, coords = _frame(6000, seed=6)
+    qm = _quantized("bevfusion", feats, coords, seed=6)
+    e = eng.Engine.from_model(qm, eng.PRECISION_INT8, 0)
+    e.forward(_dev(feats), _dev(coords), GRID)
+    torch.cuda.synchronize()
+    int8_out = e.output(0).cpu().numpy()
+    n_conv = sum(1 for nd in qm["nodes"] if nd["op"] == "conv")
+    n_add = sum(1 for nd in qm["nodes"] if nd["op"] == "add")
+    assert e.set_node_precision("SparseConvolution", eng.PRECISION_FP16, eng.PRECISION_FP16,
+                                by_optype=True) == n_conv
+    assert e.set_node_precision("Add", eng.PRECISION_FP16, eng.PRECISION_FP16,
+                                by_optype=True) == n_add
+    e.reconfigure()
+    e.forward(_dev(feats), _dev(coords), GRID)
+    torch.cuda.synchronize()
+    assert e.status()[0] == 0
+    all_fp16 = e.output(0).cpu().numpy()
+    ref = eng.Engine.from_model(qm, eng.PRECISION_FP16, 0)
+    ref.forward(_dev(feats), _dev(coords), GRID)
+    torch.cuda.synchronize()
+    assert np.array_equal(all_fp16.view(np.uint16), ref.output(0).cpu().numpy().view(np.uint16))
+    assert not np.array_equal(all_fp16.view(np.uint16), int8_out.view(np.uint16))
