@@ -240,6 +240,28 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def bind_to_gpu_cpus(index):
+    """One process per GPU: run it (and first-touch its pinned buffers) on the CPUs NVML lists
+    as local to that GPU, so that eight ranks' host copies do not all cross to one socket.
+    Best effort: any failure leaves the affinity as it was."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if visible:
+            index = int(visible.split(",")[index])
+        h = pynvml.nvmlDeviceGetHandleByIndex(index)
+        words = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(h, words)
+        cpus = {64 * w + b for w, m in enumerate(mask) for b in range(64) if (m >> b) & 1}
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+        pynvml.nvmlShutdown()
+    except Exception:
+        pass
+
+
 # ------------------------------------------------------------------ GPU arm
 def run_gpu(args, rank, world, local_rank):
     import torch
@@ -247,6 +269,8 @@ def run_gpu(args, rank, world, local_rank):
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    if world > 1:
+        bind_to_gpu_cpus(local_rank)  # before the pinned buffers are allocated
     dist = None
     if world > 1:
         import torch.distributed as dist_mod
