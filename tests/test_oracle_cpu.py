@@ -2,6 +2,7 @@
 fixtures, dense cross-correlation, the tensor container, quantisation rules."""
 import json
 import os
+import sys
 
 import numpy as np
 import pytest
@@ -185,3 +186,18 @@ def test_oracle_inverse_conv_equals_dense_transposed_conv():
                     for (b, z, y, x) in coords])
     got = u["feat"].astype(np.float64)
     assert np.abs(got - ref).max() <= 2e-3 * np.abs(ref).max()
+
+
+def test_oracle_conv_equals_gather_gemm_scatter_on_config0():
+    """Benchmark configuration 0 (20 000 voxels, 16 -> 16, fp32): the oracle's convolution
+    equals the per-offset index_select + mm + index_add_ that the PyTorch sparse-conv packages
+    run, on the same rulebook."""
+    torch = pytest.importorskip("torch")
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
+                                    "oracle"))
+    import cpu_baseline_config0 as c0
+    coords, x, w = c0.problem(3)
+    y, m, pairs = c0.run_oracle(coords, x, w)
+    assert pairs == int((m[:, :c0.N] >= 0).sum())
+    yt = c0.run_torch(torch, x, w, m)
+    assert np.abs(y - yt).max() <= 1e-5 * max(1.0, float(np.abs(yt).max()))
