@@ -514,3 +514,81 @@ def test_set_node_precision_by_optype_rebuilds_the_engine():
     torch.cuda.synchronize()
     assert np.array_equal(all_fp16.view(np.uint16), ref.output(0).cpu().numpy().view(np.uint16))
     assert not np.array_equal(all_fp16.view(np.uint16), int8_out.view(np.uint16))
+
+
+# ------------------------------------------------- full benchmark size, by properties
+def test_full_size_frame_properties_200k_voxels():
+    """The largest benchmark frame (200 000 voxels, 41x1440x1440, int8 backbone), checked by
+    properties that do not need the oracle: every coordinate set a strided rulebook makes is
+    strictly ascending in cell order (unique and sorted); every map entry points at an
+    existing input row, SubM maps hold the row itself at the centre tap and are symmetric
+    (tap k of row i = j  <=>  tap 26-k of row j = i); two forwards and a CUDA-graph replay
+    with the row count read on the device give identical bits; reading the dense output back
+    at the last coordinate set returns exactly that tensor's features."""
+    eng = _engine_mod()
+    grid = (41, 1440, 1440)
+    n = 200000
+    coords = scenes.make_coords(n, grid, 163)
+    feats = scenes.make_point_features(coords, 163)
+    model = models.scn_backbone("centerpoint", seed=0, grid_zyx=grid, output_bound=520000)
+    df, dc = _dev(feats), _dev(coords)
+    qm = models.quantize(model, eng.calibrate(model, df, dc, grid))
+    e = eng.Engine.from_model(qm, eng.PRECISION_INT8, eng.BUILD_KEEP_TENSORS)
+    e.forward(df, dc, grid)
+    torch.cuda.synchronize()
+    assert e.status()[0] == 0
+    first = e.output(0).clone()
+
+    # coordinate sets and maps
+    for m, n_out, n_in in e.rules():
+        kvol = m.shape[0]
+        mm = m[:, :n_out]
+        assert int(mm.max()) < n_in and int(mm.min()) >= -1
+        if kvol == 27 and n_out == n_in:  # SubM
+            centre = mm[13]
+            assert torch.equal(centre, torch.arange(n_out, device="cuda", dtype=torch.int32))
+            k = 5
+            rows = torch.nonzero(mm[k] >= 0).flatten()
+            back = mm[26 - k][mm[k][rows].long()]
+            assert torch.equal(back, rows.to(torch.int32))
+    last = None
+    for tid in models.tensor_ids(qm):
+        try:
+            t = e.tensor(tid)
+        except RuntimeError:
+            continue  # fused into its consumer's epilogue: never materialised
+        if t["coords"] is None:
+            continue
+        c = t["coords"][: t["n"]].long()
+        last = t
+        if tid == "0":
+            continue
+        # (b, z, y, x) lexicographic order = cell order in any grid
+        key = ((c[:, 0] * 64 + c[:, 1]) * 2048 + c[:, 2]) * 2048 + c[:, 3]
+        assert bool((key[1:] > key[:-1]).all()), "tensor %s rows not strictly ascending" % tid
+
+    # dense output read back at the last sparse tensor's coordinates
+    t = last
+    c = t["coords"][: t["n"]].long()
+    dense5 = first.view(1, 128, 2, 180, 180)
+    got = dense5[0, :, c[:, 1], c[:, 2], c[:, 3]].t().contiguous()
+    assert torch.equal(got.view(torch.int16), t["features"][: t["n"]].view(torch.int16))
+    assert int((first != 0).any(dim=1).sum()) <= t["n"]
+
+    # determinism, and the graph path with a device-side row count
+    e.forward(df, dc, grid)
+    torch.cuda.synchronize()
+    assert torch.equal(e.output(0), first)
+    e2 = eng.Engine.from_model(qm, eng.PRECISION_INT8, 0)
+    n_dev = torch.tensor([n], dtype=torch.int32, device="cuda")
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        e2.forward_dds(df, dc, n_dev, grid, stream=stream)
+        stream.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            e2.forward_dds(df, dc, n_dev, grid, stream=stream)
+        g.replay()
+        stream.synchronize()
+    assert e2.status()[0] == 0
+    assert torch.equal(e2.output(0), first)
