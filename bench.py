@@ -443,12 +443,22 @@ def run_gpu(args, rank, world, local_rank):
                          "hbm_frac_of_measured": tot_bytes / frame_s / 1e9 / peak,
                          "serial_kernel_ms": all_ms}
         if args.profile_table:
+            # per step: time, algorithmic bytes and useful ops, the roofline time (the larger of
+            # bytes / measured HBM copy bandwidth and ops / tensor peak: int8 at the nominal
+            # 4 500 TOPS, fp16 at the measured bf16 cuBLAS rate) and the fraction of it achieved
+            tensor_i8 = 4500e12
+            tensor_f16 = float(peaks.get("bf16_tflops", 1590.0)) * 1e12
             with open(args.profile_table, "w") as f:
                 for ln, ms in prof:
                     ops, nbytes = step_work(ln, prof_engine.coordset_rows, lambda r: pairs[r],
                                             dense_elems)
-                    f.write("%8.2f us  %8.3f MB  %8.3f GOP  %s\n" % (ms * 1000, nbytes / 1e6,
-                                                                   ops / 1e9, ln))
+                    t_hbm = nbytes / (peak * 1e9)
+                    t_tc = ops / (tensor_i8 if " in=i8 " in ln else tensor_f16)
+                    bound_us = 1e6 * max(t_hbm, t_tc)
+                    f.write("%8.2f us  %8.3f MB  %8.3f GOP  %6.2f us %s  %5.3f  %s\n" % (
+                        ms * 1000, nbytes / 1e6, ops / 1e9, bound_us,
+                        "hbm" if t_hbm >= t_tc else "tc ", bound_us / (ms * 1000) if ms else 0.0,
+                        ln))
         prof_engine.close()
 
         # ---- CPU baseline on the host cores of this box (bounded sample)
