@@ -267,6 +267,28 @@ SPCONVB_API int spconvb_scatter_dense(const void* feat, int32_t in_kind, float i
                                       const int32_t grid[3], const int32_t perm[3], void* out,
                                       void* stream);
 
+/* ScatterDense into one of the engine's output layouts, optionally quantised to int8
+ * (EngineBuilder::push_dense with output_layout and input_dynamic_range, engine.hpp:114-123;
+ * enum TensorLayout, engine.hpp:26).  With (s0, s1, s2) the cell after perm, C = channels,
+ * D = grid[perm0] and m = c * D + s0 the channel of the [N, C*D, H, W] view the backbones
+ * reshape to:
+ *   layout 1 NCHW    out[b][m][s1][s2]
+ *   layout 2 NCHW32  out[b][m / 32][s1][s2][m % 32], C*D padded up to a multiple of 32
+ *   layout 3 NHWzC   out[b][s1][s2][s0][c]
+ * out_kind SPCONVB_F16 or SPCONVB_I8; int8 values are clamp(rint(x * inv_out_scale)) with
+ * inv_out_scale = 127 / input_dynamic_range.  out holds spconvb_dense_bytes() bytes and is
+ * fully written.  The engine is closed, so the two vectorised layouts follow the usual
+ * meaning of their names (TensorRT's CHW32; height, width, z, channel). */
+SPCONVB_API int spconvb_scatter_dense_layout(const void* feat, int32_t in_kind, float in_scale,
+                                             const int32_t* coords, const uint32_t* n_ptr,
+                                             uint32_t launch_rows, int32_t channels,
+                                             int32_t batch, const int32_t grid[3],
+                                             const int32_t perm[3], int32_t layout,
+                                             int32_t out_kind, float inv_out_scale, void* out,
+                                             void* stream);
+SPCONVB_API size_t spconvb_dense_bytes(int32_t channels, int32_t batch, const int32_t grid[3],
+                                       const int32_t perm[3], int32_t layout, int32_t out_kind);
+
 /* -------------------------------------------------------------- voxelizer
  * Replaces buildHashKernel / voxelizationKernel / featureExtractionKernel
  * (CUDA-CenterPoint/src/preprocess_kernels.cu:70-173 and the two copies in
@@ -413,6 +435,15 @@ SPCONVB_API int spconvb_engine_num_outputs(const spconvb_engine* e);
 SPCONVB_API int spconvb_engine_output(const spconvb_engine* e, int i, void** data,
                                       int64_t shape[8], int32_t* ndim, int32_t* kind,
                                       int32_t* dense);
+
+/* Memory layout of dense output i: the TensorLayout value (1 NCHW, 2 NCHW32, 3 NHWzC; 0 for
+ * a sparse output), the dimensions as they lie in memory (NCHW32: {N, ceil(C*D/32), H, W, 32};
+ * NHWzC: {N, H, W, D, C}; NCHW: the shape spconvb_engine_output reports) and the byte size.
+ * spconvb_engine_output keeps reporting the logical NCHW shape, as
+ * SparseDTensor::features().shape does (engine.hpp:38-50). */
+SPCONVB_API int spconvb_engine_output_layout(const spconvb_engine* e, int i, int32_t* layout,
+                                             int64_t physical_shape[8], int32_t* ndim,
+                                             size_t* bytes);
 
 /* Any tensor by name (needs SPCONVB_BUILD_KEEP_TENSORS for intermediates):
  * features pointer, element kind, channels as stored, int8 scale, coordinates

@@ -75,6 +75,10 @@ SYMBOLS = {
                                   _VP, C.c_uint32, _VP, _VP]),
     "spconvb_scatter_dense": (C.c_int, [_VP, C.c_int32, C.c_float, _VP, _VP, C.c_uint32,
                                         C.c_int32, C.c_int32, _I3, _I3, _VP, _VP]),
+    "spconvb_scatter_dense_layout": (C.c_int, [_VP, C.c_int32, C.c_float, _VP, _VP, C.c_uint32,
+                                               C.c_int32, C.c_int32, _I3, _I3, C.c_int32,
+                                               C.c_int32, C.c_float, _VP, _VP]),
+    "spconvb_dense_bytes": (C.c_size_t, [C.c_int32, C.c_int32, _I3, _I3, C.c_int32, C.c_int32]),
     "spconvb_voxelize_workspace_bytes": (C.c_size_t, [C.POINTER(VoxelParams), C.c_uint32]),
     "spconvb_voxelize": (C.c_int, [C.POINTER(VoxelParams), _VP, C.c_uint32, _VP, _VP, _VP, _VP,
                                    _VP, _VP]),

@@ -196,6 +196,59 @@ __global__ void scatter_dense_kernel(const void* __restrict__ feat, int in_kind,
   }
 }
 
+// ScatterDense into the vectorised layouts and/or int8.  One thread per (row, channel): reads
+// are coalesced along the row, writes land in the 32-channel (NCHW32) or C-channel (NHWzC)
+// group of the voxel's cell.  With m = channel * g(p0) + s0 the channel of the [N, C*D, H, W]
+// view:  NCHW   out[b][m][s1][s2]
+//        NCHW32 out[b][m / 32][s1][s2][m % 32]      (channel count padded up to 32)
+//        NHWzC  out[b][s1][s2][s0][channel]
+template <typename OutT>
+__global__ void scatter_dense_layout_kernel(const void* __restrict__ feat, int in_kind,
+                                            float in_scale, const int4* __restrict__ coords,
+                                            const uint32_t* n_ptr, int channels, Grid3 g, int p0,
+                                            int p1, int p2, int layout, float inv_out,
+                                            int copy_bytes, OutT* __restrict__ out) {
+  const size_t total = (size_t)(*n_ptr) * channels;
+  const int g0 = g.g[p0], g1 = g.g[p1], g2 = g.g[p2];
+  const long long plane = (long long)g1 * g2;
+  const long long merged = (long long)channels * g0;
+  const long long blocks32 = (merged + 31) / 32;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (size_t)gridDim.x * blockDim.x) {
+    const size_t row = i / channels;
+    const int ch = (int)(i % channels);
+    const int4 c = coords[row];
+    const int sp[3] = {c.y, c.z, c.w};
+    const int s0 = sp[p0], s1 = sp[p1], s2 = sp[p2];
+    if ((unsigned)c.x >= (unsigned)g.batch || (unsigned)s0 >= (unsigned)g0 ||
+        (unsigned)s1 >= (unsigned)g1 || (unsigned)s2 >= (unsigned)g2)
+      continue;
+    const long long m = (long long)ch * g0 + s0;
+    long long dst;
+    if (layout == 2)
+      dst = (((long long)c.x * blocks32 + m / 32) * plane + (long long)s1 * g2 + s2) * 32 + m % 32;
+    else if (layout == 3)
+      dst = ((((long long)c.x * g1 + s1) * g2 + s2) * g0 + s0) * channels + ch;
+    else
+      dst = ((long long)c.x * merged + m) * plane + (long long)s1 * g2 + s2;
+    if (sizeof(OutT) == 1) {
+      int8_t q;
+      if (in_kind == SPCONVB_I8) {
+        const int8_t v = ((const int8_t*)feat)[i];
+        q = copy_bytes ? v : (int8_t)sat8(__fmul_rn(__fmul_rn((float)v, in_scale), inv_out));
+      } else {
+        q = (int8_t)sat8(__fmul_rn(__half2float(((const __half*)feat)[i]), inv_out));
+      }
+      ((int8_t*)out)[dst] = q;
+    } else {
+      ((__half*)out)[dst] =
+          in_kind == SPCONVB_I8
+              ? __float2half_rn(__fmul_rn((float)((const int8_t*)feat)[i], in_scale))
+              : ((const __half*)feat)[i];
+    }
+  }
+}
+
 static inline uint32_t clamp_u32(size_t v) { return v > 0xffffffffull ? 0xffffffffu : (uint32_t)v; }
 
 }  // namespace spconvb
@@ -291,6 +344,60 @@ int spconvb_scatter_dense(const void* feat, int32_t in_kind, float in_scale,
       (__half*)out);
   SPCONVB_LAUNCH_CHECK();
   return SPCONVB_OK;
+}
+
+int spconvb_scatter_dense_layout(const void* feat, int32_t in_kind, float in_scale,
+                                 const int32_t* coords, const uint32_t* n_ptr,
+                                 uint32_t launch_rows, int32_t channels, int32_t batch,
+                                 const int32_t grid[3], const int32_t perm[3], int32_t layout,
+                                 int32_t out_kind, float inv_out_scale, void* out, void* stream) {
+  if (layout == 0) layout = 1;
+  if (layout == 1 && out_kind == SPCONVB_F16)
+    return spconvb_scatter_dense(feat, in_kind, in_scale, coords, n_ptr, launch_rows, channels,
+                                 batch, grid, perm, out, stream);
+  if (!feat || !coords || !n_ptr || !grid || !out || channels < 1 || channels > 1024 ||
+      batch < 1 || launch_rows < 1 || layout < 1 || layout > 3 ||
+      (out_kind != SPCONVB_F16 && out_kind != SPCONVB_I8) ||
+      (in_kind != SPCONVB_F16 && in_kind != SPCONVB_I8))
+    return SPCONVB_E_ARG;
+  if (out_kind == SPCONVB_I8 && !(inv_out_scale > 0.f)) return SPCONVB_E_ARG;
+  int p[3] = {0, 1, 2};
+  if (perm) {
+    p[0] = perm[0]; p[1] = perm[1]; p[2] = perm[2];
+    if ((1 << p[0] | 1 << p[1] | 1 << p[2]) != 7) return SPCONVB_E_ARG;
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  Grid3 g;
+  g.g[0] = grid[0]; g.g[1] = grid[1]; g.g[2] = grid[2];
+  g.batch = batch;
+  const size_t bytes = spconvb_dense_bytes(channels, batch, grid, perm, layout, out_kind);
+  SPCONVB_CUDA_TRY(cudaMemsetAsync(out, 0, bytes, st));
+  // int8 rows stored with the scale the dense tensor is asked in are copied byte for byte
+  const int copy_bytes = in_kind == SPCONVB_I8 && out_kind == SPCONVB_I8 &&
+                         fabsf(in_scale * inv_out_scale - 1.f) < 1e-6f;
+  const uint32_t work = clamp_u32((size_t)launch_rows * channels);
+  const int blocks = blocks_for(work, 256);
+  if (out_kind == SPCONVB_I8)
+    scatter_dense_layout_kernel<int8_t><<<blocks, 256, 0, st>>>(
+        feat, in_kind, in_scale, (const int4*)coords, n_ptr, channels, g, p[0], p[1], p[2], layout,
+        inv_out_scale, copy_bytes, (int8_t*)out);
+  else
+    scatter_dense_layout_kernel<__half><<<blocks, 256, 0, st>>>(
+        feat, in_kind, in_scale, (const int4*)coords, n_ptr, channels, g, p[0], p[1], p[2], layout,
+        inv_out_scale, 0, (__half*)out);
+  SPCONVB_LAUNCH_CHECK();
+  return SPCONVB_OK;
+}
+
+size_t spconvb_dense_bytes(int32_t channels, int32_t batch, const int32_t grid[3],
+                           const int32_t perm[3], int32_t layout, int32_t out_kind) {
+  if (!grid || channels < 1 || batch < 1) return 0;
+  const int p0 = perm ? perm[0] : 0;
+  if (p0 < 0 || p0 > 2) return 0;
+  size_t merged = (size_t)channels * grid[p0];
+  if (layout == 2) merged = (merged + 31) / 32 * 32;
+  const size_t cells = (size_t)grid[0] * grid[1] * grid[2] / grid[p0];
+  return (size_t)batch * merged * cells * (out_kind == SPCONVB_I8 ? 1 : 2);
 }
 
 }  // extern "C"

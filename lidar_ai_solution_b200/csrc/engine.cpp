@@ -545,9 +545,9 @@ int Engine::compile(const Builder& b, int precision, uint32_t build_flags, cudaS
       case OP_DENSE: {
         const int a = g2r[n.in0];
         if (a < 0 || rt[a].dense) return SPCONVB_E_ARG;
-        if (n.layout != 1) {
-          log_msg(LOG_ERROR, "dense '%s': only the NCHW output layout is implemented", n.name.c_str());
-          return SPCONVB_E_UNSUPPORTED;
+        if (n.layout < 1 || n.layout > 3) {
+          log_msg(LOG_ERROR, "dense '%s': unknown output layout %d", n.name.c_str(), n.layout);
+          return SPCONVB_E_ARG;
         }
         Step s;
         s.kind = Step::DENSE;
@@ -560,6 +560,7 @@ int Engine::compile(const Builder& b, int precision, uint32_t build_flags, cudaS
         // a Reshape only renames the shape.
         std::vector<int64_t> shape;
         for (int v : n.out_shape) shape.push_back(v);
+        std::vector<int64_t> shape5 = shape;  // the scatter's own (permuted) shape
         int cur = n.out;
         while (true) {
           const GTensor& t = b.tensors[cur];
@@ -573,6 +574,7 @@ int Engine::compile(const Builder& b, int precision, uint32_t build_flags, cudaS
             std::vector<int64_t> ns = shape;
             for (int a2 = 0; a2 < 3; ++a2) { s.perm[a2] = p[a2]; ns[2 + a2] = shape[2 + p[a2]]; }
             shape = ns;
+            shape5 = ns;
             s.has_perm = true;
           } else if (cn.op == OP_RESHAPE) {
             int64_t total = 1, known = 1;
@@ -596,9 +598,32 @@ int Engine::compile(const Builder& b, int precision, uint32_t build_flags, cudaS
           dead[c] = 1;
           cur = cn.out;
         }
-        s.out = new_rt(b.tensors[cur].name, s.cs, s.cout, SPCONVB_F16, 0.f);
+        // input_dynamic_range switches the dense tensor to int8 with that range
+        const bool i8_out = n.dense_dr > 0.f;
+        s.layout = n.layout;
+        s.inv_out = i8_out ? 127.0f / n.dense_dr : 1.f;
+        if (s.layout != 1) {
+          // the vectorised layouts are defined on the [N, C*D, H, W] view of the scatter
+          const bool ok5 = shape.size() == 5;
+          const bool ok4 = shape.size() == 4 && shape5.size() == 5 && shape[0] == shape5[0] &&
+                           shape[1] == shape5[1] * shape5[2] && shape[2] == shape5[3] &&
+                           shape[3] == shape5[4];
+          if (!ok5 && !ok4) {
+            log_msg(LOG_ERROR, "dense '%s': layout %d needs the [N,C,D,H,W] tensor or its [N,C*D,H,W] view",
+                    n.name.c_str(), s.layout);
+            return SPCONVB_E_UNSUPPORTED;
+          }
+        }
+        s.out = new_rt(b.tensors[cur].name, s.cs, s.cout, i8_out ? SPCONVB_I8 : SPCONVB_F16,
+                       i8_out ? n.dense_dr : 0.f);
         rt[s.out].dense = true;
         rt[s.out].shape = shape;
+        rt[s.out].layout = s.layout;
+        rt[s.out].phys_shape = shape;
+        if (s.layout == 2)
+          rt[s.out].phys_shape = {shape5[0], (shape5[1] * shape5[2] + 31) / 32, shape5[3], shape5[4], 32};
+        else if (s.layout == 3)
+          rt[s.out].phys_shape = {shape5[0], shape5[3], shape5[4], shape5[2], shape5[1]};
         g2r[cur] = s.out;
         steps.push_back(s);
         const int si = (int)steps.size() - 1;
@@ -749,8 +774,8 @@ int Engine::prepare(const int32_t grid[3], int batch) {
     if (t.external || t.alias_of >= 0) continue;
     if (t.dense) {
       size_t numel = 1;
-      for (auto v : t.shape) numel *= (size_t)v;
-      t.bytes = numel * sizeof(uint16_t);
+      for (auto v : t.phys_shape) numel *= (size_t)v;
+      t.bytes = numel * (t.kind == SPCONVB_I8 ? 1 : sizeof(uint16_t));
     } else {
       t.bytes = (size_t)coordsets[t.cs].cap * t.channels * (t.kind == SPCONVB_I8 ? 1 : 2);
     }
@@ -886,9 +911,10 @@ int Engine::forward(const void* features, const int32_t* indices, uint32_t cap_r
         break;
       case Step::DENSE: {
         const CoordSet& cs = coordsets[s.cs];
-        rc = spconvb_scatter_dense(rt[s.in0].data, rt[s.in0].kind, s.a_scale, cs_coords(s.cs),
-                                   cs_n(s.cs), cs_launch(s.cs), s.cout, batch, cs.grid,
-                                   s.has_perm ? s.perm : nullptr, rt[s.out].data, st);
+        rc = spconvb_scatter_dense_layout(rt[s.in0].data, rt[s.in0].kind, s.a_scale,
+                                          cs_coords(s.cs), cs_n(s.cs), cs_launch(s.cs), s.cout,
+                                          batch, cs.grid, s.has_perm ? s.perm : nullptr, s.layout,
+                                          rt[s.out].kind, s.inv_out, rt[s.out].data, st);
         last_launches += 1;
         break;
       }

@@ -100,7 +100,9 @@ struct RTensor {
   bool external = false;
   bool is_output = false;
   int alias_of = -1;         // shares the buffer of another tensor (Reshape)
-  std::vector<int64_t> shape;  // dense shape
+  std::vector<int64_t> shape;  // dense shape (logical, NCHW order)
+  int layout = 1;              // dense: physical TensorLayout
+  std::vector<int64_t> phys_shape;  // dense: dimensions as laid out in memory
   int first_step = 1 << 30, last_step = -1;
   void* data = nullptr;
   size_t bytes = 0;
@@ -126,6 +128,7 @@ struct Step {
   float a_scale = 1.f, b_scale = 1.f, inv_out = 1.f;
   int perm[3] = {0, 1, 2};
   bool has_perm = false;
+  int layout = 1;             // dense: TensorLayout of the output
 };
 
 struct Profile {

@@ -241,6 +241,8 @@ int spconvb_onnx_inspect(const char* path, char* buf, size_t buf_bytes) {
     } else if (n.op == OP_DENSE) {
       out += " format=" + n.format + " out_shape=";
       for (int v : n.out_shape) out += std::to_string(v) + ",";
+      snprintf(line, sizeof(line), " layout=%d in_dr=%.9g", n.layout, (double)n.dense_dr);
+      out += line;
     } else if (n.op == OP_RESHAPE || n.op == OP_TRANSPOSE) {
       out += " dims=";
       for (auto v : n.dims) out += std::to_string(v) + ",";
@@ -400,6 +402,21 @@ int spconvb_engine_output(const spconvb_engine* e, int i, void** data, int64_t s
     nd = 2;
   }
   if (ndim) *ndim = nd;
+  return SPCONVB_OK;
+}
+
+int spconvb_engine_output_layout(const spconvb_engine* e, int i, int32_t* layout,
+                                 int64_t physical_shape[8], int32_t* ndim, size_t* bytes) {
+  if (!e || i < 0 || i >= (int)e->e->outputs.size()) return SPCONVB_E_ARG;
+  const RTensor& t = e->e->rt[e->e->outputs[i]];
+  if (layout) *layout = t.dense ? t.layout : 0;
+  int nd = 0;
+  if (t.dense) {
+    for (auto v : t.phys_shape)
+      if (nd < 8 && physical_shape) physical_shape[nd++] = v;
+  }
+  if (ndim) *ndim = nd;
+  if (bytes) *bytes = t.bytes;
   return SPCONVB_OK;
 }
 

@@ -112,7 +112,22 @@ class Engine:
         ndim, kind, dense = C.c_int32(), C.c_int32(), C.c_int32()
         cabi.check(self._lib.spconvb_engine_output(self._h, i, C.byref(data), shape,
                                                    C.byref(ndim), C.byref(kind), C.byref(dense)))
+        layout, pshape, pnd, _ = self._output_layout(i)
+        if layout > 1:  # NCHW32 / NHWzC: the view has the dimensions as they lie in memory
+            return _view(data.value, pshape, kind.value, self.device)
         return _view(data.value, [shape[d] for d in range(ndim.value)], kind.value, self.device)
+
+    def _output_layout(self, i):
+        layout, nd, nbytes = C.c_int32(), C.c_int32(), C.c_size_t()
+        pshape = (C.c_int64 * 8)()
+        cabi.check(self._lib.spconvb_engine_output_layout(self._h, i, C.byref(layout), pshape,
+                                                          C.byref(nd), C.byref(nbytes)))
+        return layout.value, [pshape[d] for d in range(nd.value)], nd.value, nbytes.value
+
+    def output_layout(self, i=0):
+        """Name of the TensorLayout of dense output ``i`` ("NCHW", "NCHW32", "NHWzC"; "None"
+        for a sparse output)."""
+        return ["None", "NCHW", "NCHW32", "NHWzC"][self._output_layout(i)[0]]
 
     def output_ptr(self, i=0):
         data = C.c_void_p()
@@ -120,6 +135,8 @@ class Engine:
         ndim, kind, dense = C.c_int32(), C.c_int32(), C.c_int32()
         cabi.check(self._lib.spconvb_engine_output(self._h, i, C.byref(data), shape,
                                                    C.byref(ndim), C.byref(kind), C.byref(dense)))
+        if dense.value:
+            return data.value, self._output_layout(i)[3]
         nbytes = int(np.prod([shape[d] for d in range(ndim.value)])) * (1 if kind.value else 2)
         return data.value, nbytes
 

@@ -124,9 +124,13 @@ def serialize(model: dict) -> bytes:
         elif op == "relu":
             nodes.append(_node("Relu", [nd["x"]], [nd["out"]], nd["name"], {}))
         elif op == "dense":
-            nodes.append(_node("ScatterDense", [nd["x"]], [nd["out"]], nd["name"], {
-                "input_spatial_shape": list(nd["input_spatial_shape"]), "format": nd["format"],
-                "output_shape": list(nd["output_shape"])}))
+            attrs = {"input_spatial_shape": list(nd["input_spatial_shape"]),
+                     "format": nd["format"], "output_shape": list(nd["output_shape"])}
+            if nd.get("output_layout"):
+                attrs["output_layout"] = nd["output_layout"]
+            if nd.get("input_dynamic_range"):
+                attrs["input_dynamic_range"] = float(nd["input_dynamic_range"])
+            nodes.append(_node("ScatterDense", [nd["x"]], [nd["out"]], nd["name"], attrs))
         elif op == "reshape":
             nodes.append(_node("Reshape", [nd["x"]], [nd["out"]], nd["name"],
                                {"dims": list(nd["dims"])}))

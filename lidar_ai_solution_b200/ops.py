@@ -205,6 +205,35 @@ def scatter_dense(feat, coords, n_ptr, grid, batch=1, in_scale=1.0, perm=None):
     return out
 
 
+LAYOUTS = {"NCHW": 1, "NCHW32": 2, "NHWzC": 3}
+
+
+def scatter_dense_layout(feat, coords, n_ptr, grid, layout="NCHW", dynamic_range=0.0, batch=1,
+                         in_scale=1.0, perm=None):
+    """ScatterDense into ``layout``; int8 with scale ``dynamic_range / 127`` when the range is
+    positive, else fp16.  Returns the tensor with the dimensions as they lie in memory."""
+    ch = feat.shape[1]
+    g = [grid[p] for p in perm] if perm is not None else list(grid)
+    lay = LAYOUTS[layout]
+    i8 = dynamic_range > 0
+    if lay == 2:
+        shape = (batch, (ch * g[0] + 31) // 32, g[1], g[2], 32)
+    elif lay == 3:
+        shape = (batch, g[1], g[2], g[0], ch)
+    else:
+        shape = (batch, ch, g[0], g[1], g[2])
+    out = torch.empty(shape, dtype=torch.int8 if i8 else torch.float16, device=feat.device)
+    lib = cabi.lib()
+    pp = cabi.i3(perm) if perm is not None else None
+    assert lib.spconvb_dense_bytes(ch, batch, cabi.i3(grid), pp, lay, 1 if i8 else 0) == \
+        out.numel() * out.element_size()
+    inv = float(np.float32(127.0) / np.float32(dynamic_range)) if i8 else 1.0
+    cabi.check(lib.spconvb_scatter_dense_layout(
+        _ptr(feat), kind_of(feat), in_scale, _ptr(coords), _ptr(n_ptr), feat.shape[0], ch, batch,
+        cabi.i3(grid), pp, lay, 1 if i8 else 0, inv, _ptr(out), _stream()), "scatter_dense_layout")
+    return out
+
+
 def voxel_params(prange, vsize, grid_xyz, num_features=5, points_kind=0, max_pts=10,
                  max_voxels=160000, order=0):
     p = cabi.VoxelParams()

@@ -83,6 +83,7 @@ def run(model, features, coords, grid, precision="fp16"):
     T = {model["inputs"][0][0]: dict(feat=np.ascontiguousarray(features, np.float16), coords=coords,
                                      grid=list(grid), kind="f16", dr=0.0)}
     dense = {}
+    dense_meta = {}
     rule_cache = {}
     named_rules = {}
     for n in model["nodes"]:
@@ -159,12 +160,28 @@ def run(model, features, coords, grid, precision="fp16"):
         elif op == "dense":
             a = T[n["x"]]
             s = float(F32(a["dr"]) / F32(127.0)) if a["kind"] == "i8" else 1.0
-            dense[n["out"]] = orc.scatter_dense(a["feat"], a["coords"], a["grid"], 1, s)
+            ddr = float(n.get("input_dynamic_range", 0.0) or 0.0)
+            if ddr > 0:  # int8 dense tensor with that range
+                if a["kind"] == "i8" and a["dr"] == ddr:
+                    q = a["feat"]
+                elif a["kind"] == "i8":  # stored with another range: rescale in fp32
+                    inv = F32(127.0) / F32(ddr)
+                    q = np.clip(np.rint((a["feat"].astype(np.float32) * F32(s)) * inv),
+                                -128, 127).astype(np.int8)
+                else:
+                    q = orc.quantize_f16(a["feat"], ddr)
+                dense[n["out"]] = orc.scatter_dense_i8(q, a["coords"], a["grid"], 1)
+            else:
+                dense[n["out"]] = orc.scatter_dense(a["feat"], a["coords"], a["grid"], 1, s)
+            dense_meta[n["out"]] = (n.get("output_layout", "NCHW"), a["feat"].shape[1])
         elif op == "transpose":
             dense[n["out"]] = np.ascontiguousarray(np.transpose(dense[n["x"]], n["dims"]))
+            dense_meta[n["out"]] = dense_meta[n["x"]]
         elif op == "reshape":
             dense[n["out"]] = dense[n["x"]].reshape(n["dims"])
+            dense_meta[n["out"]] = dense_meta[n["x"]]
         else:
             raise ValueError(op)
-    outs = [dense[o] if o in dense else T[o]["feat"] for o, _ in model["outputs"]]
+    outs = [orc.dense_layout(dense[o], *dense_meta[o]) if o in dense else T[o]["feat"]
+            for o, _ in model["outputs"]]
     return outs, T

@@ -181,6 +181,44 @@ def scatter_dense(feat, coords, grid, batch=1, in_scale=1.0, perm=None):
     return out
 
 
+def scatter_dense_i8(featq, coords, grid, batch=1, perm=None):
+    """int8 rows scattered into a zero int8 [batch, C, g(p0), g(p1), g(p2)] tensor (rows outside
+    the grid are dropped; coordinates are unique)."""
+    featq = np.ascontiguousarray(featq, np.int8)
+    coords = np.asarray(coords, np.int64)
+    p = list(perm) if perm is not None else [0, 1, 2]
+    g = [grid[a] for a in p]
+    out = np.zeros((batch, featq.shape[1], g[0], g[1], g[2]), np.int8)
+    sp = coords[:, 1:4][:, p]
+    ok = (coords[:, 0] >= 0) & (coords[:, 0] < batch)
+    for a in range(3):
+        ok &= (sp[:, a] >= 0) & (sp[:, a] < g[a])
+    b, s0, s1, s2 = coords[ok, 0], sp[ok, 0], sp[ok, 1], sp[ok, 2]
+    out[b, :, s0, s1, s2] = featq[ok]
+    return out
+
+
+def dense_layout(dense, layout, channels):
+    """Physical arrangement of a dense [N, C, D, H, W] tensor (or its [N, C*D, H, W] view) in
+    one of the engine's TensorLayout values (engine.hpp:26): "NCHW" leaves it as it is,
+    "NCHW32" is [N, ceil(C*D/32), H, W, 32] with zero padding, "NHWzC" is [N, H, W, D, C]."""
+    if layout in ("NCHW", "", None):
+        return dense
+    n = dense.shape[0]
+    h, w = dense.shape[-2], dense.shape[-1]
+    merged = dense.reshape(n, -1, h, w)
+    m = merged.shape[1]
+    if layout == "NCHW32":
+        mb = (m + 31) // 32
+        pad = np.zeros((n, mb * 32, h, w), dense.dtype)
+        pad[:, :m] = merged
+        return np.ascontiguousarray(pad.reshape(n, mb, 32, h, w).transpose(0, 1, 3, 4, 2))
+    if layout == "NHWzC":
+        d = m // channels
+        return np.ascontiguousarray(merged.reshape(n, channels, d, h, w).transpose(0, 3, 4, 2, 1))
+    raise ValueError(layout)
+
+
 def voxelize(points, range6, vsize, gridxyz, max_voxels=160000, max_pts=10, order=0):
     """points: [n, nfeat] float32 or float16.  Returns (features f16, coords i32, total)."""
     points = np.ascontiguousarray(points)

@@ -122,6 +122,39 @@ def test_int8_backbone_exact_with_cuda_core_fp16_layers(kind, fusion):
     assert np.array_equal(e.output(0).cpu().numpy().view(np.uint16), outs[0].view(np.uint16))
 
 
+@pytest.mark.parametrize("kind,layout,int8_out", [
+    ("centerpoint", "NCHW32", True), ("centerpoint", "NHWzC", True), ("centerpoint", "NCHW", True),
+    ("bevfusion", "NCHW32", True), ("bevfusion", "NHWzC", False), ("centerpoint", "NCHW32", False)])
+def test_dense_output_layouts_through_the_engine(kind, layout, int8_out, tmp_path):
+    """ScatterDense with output_layout and input_dynamic_range (EngineBuilder::push_dense):
+    the dense output leaves the engine in NCHW / NCHW32 / NHWzC, int8 when the node carries
+    a dynamic range, identical to the oracle's relayout of its own dense tensor."""
+    eng = _engine_mod()
+    feats, coords = _frame(9000, seed=4)
+    model = _small_model(kind, 4)
+    ranges = eng.calibrate(model, _dev(feats), _dev(coords), GRID)
+    model = models.quantize(model, ranges)
+    dense = [n for n in model["nodes"] if n["op"] == "dense"][0]
+    dense["output_layout"] = layout
+    if int8_out:
+        producer = [n for n in model["nodes"] if n.get("out") == dense["x"]][0]
+        producer["output_precision"] = "int8"
+        dense["input_dynamic_range"] = float(ranges[dense["x"]])
+    outs, _ = graph_oracle.run(model, feats, coords, GRID, "int8")
+    e = eng.Engine.from_model(model, eng.PRECISION_INT8, eng.BUILD_FORCE_SIMT)
+    e.forward(_dev(feats), _dev(coords), GRID)
+    torch.cuda.synchronize()
+    assert e.status()[0] == 0
+    got = e.output(0).cpu().numpy()
+    assert e.output_layout(0) == layout
+    assert got.dtype == (np.int8 if int8_out else np.float16)
+    assert got.shape == outs[0].shape
+    assert np.array_equal(got.view(np.uint8), outs[0].view(np.uint8))
+    assert e.output_ptr(0)[1] == got.nbytes
+    if int8_out:
+        assert np.count_nonzero(got) > 0
+
+
 def _replay_layers(model, e, precision, in_coords):
     """Per-layer parity on the tensor-core path: every conv (+Add+Relu) is re-run on the
     oracle from the engine's own input tensors; int8 results must be identical, fp16 within

@@ -95,6 +95,17 @@ def test_onnx_writer_and_reader_round_trip(tmp_path):
     assert any(ln.startswith("Transpose") and "dims=0,1,2,4,3," in ln for ln in lines)
     assert lines[-1] == "Output %s" % qm["outputs"][0][0]
     assert "Reshape" in lines[-2] and "dims=1,256,180,180," in lines[-2]
+    dense = [ln for ln in lines if ln.startswith("ScatterDense")]
+    assert len(dense) == 1 and dense[0].endswith(" layout=1 in_dr=0")
+    # output_layout and input_dynamic_range of ScatterDense survive the file
+    for layout, code in (("NCHW32", 2), ("NHWzC", 3)):
+        m2 = dict(qm, nodes=[dict(n) for n in qm["nodes"]])
+        d = [n for n in m2["nodes"] if n["op"] == "dense"][0]
+        d["output_layout"], d["input_dynamic_range"] = layout, 4.25
+        onnx_writer.save(m2, path)
+        rc, text = _inspect(lib, path)
+        assert rc == 0
+        assert (" layout=%d in_dr=4.25" % code) in text
 
 
 def test_loader_error_codes(tmp_path):

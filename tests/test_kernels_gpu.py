@@ -395,6 +395,41 @@ def test_scatter_dense(perm, kind):
     assert np.array_equal(out.cpu().numpy().view(np.uint16), ref.view(np.uint16))
 
 
+@pytest.mark.parametrize("perm", [None, (2, 0, 1)])
+@pytest.mark.parametrize("in_kind,dynamic_range", [(0, 0.0), (0, 2.5), (1, 0.0), (1, 2.54), (1, 3.0)])
+@pytest.mark.parametrize("layout,ch", [("NCHW", 128), ("NCHW32", 128), ("NCHW32", 24), ("NHWzC", 128),
+                                       ("NHWzC", 24)])
+def test_scatter_dense_layouts(layout, ch, in_kind, dynamic_range, perm):
+    """Dense outputs in the engine's three layouts, fp16 or int8 (input_dynamic_range > 0):
+    bit-exact against the restatement, padding channels and empty cells zero.  The int8 rows
+    carry the scale 0.02 = 2.54 / 127, so the range 2.54 is the byte-copy case and 3.0 the
+    rescaling one."""
+    ops = _ops()
+    grid, n = (2, 90, 100), 5000
+    coords = scenes.make_coords(n, grid, 2)
+    rng = np.random.default_rng(1)
+    feat = (rng.integers(-128, 128, (n, ch)).astype(np.int8) if in_kind
+            else rng.standard_normal((n, ch)).astype(np.float16))
+    in_scale = float(np.float32(2.54) / np.float32(127.0)) if in_kind else 1.0
+    if dynamic_range > 0:
+        if in_kind and dynamic_range == 2.54:
+            q = feat
+        elif in_kind:
+            inv = np.float32(127.0) / np.float32(dynamic_range)
+            q = np.clip(np.rint((feat.astype(np.float32) * np.float32(in_scale)) * inv),
+                        -128, 127).astype(np.int8)
+        else:
+            q = orc.quantize_f16(feat, dynamic_range)
+        ref = orc.scatter_dense_i8(q, coords, grid, 1, perm)
+    else:
+        ref = orc.scatter_dense(feat, coords, grid, 1, in_scale, perm)
+    ref = orc.dense_layout(ref, layout, ch)
+    out = ops.scatter_dense_layout(_dev(feat), _dev(coords), ops.device_count(n), grid, layout,
+                                   dynamic_range, 1, in_scale, perm).cpu().numpy()
+    assert out.shape == ref.shape and out.dtype == ref.dtype
+    assert np.array_equal(out.view(np.uint8), ref.view(np.uint8))
+
+
 # ------------------------------------------------------------------ voxelizer
 @pytest.mark.parametrize("kind", ["f32", "f16"])
 def test_voxelizer_matches_sequential_reference(kind, golden_dir):

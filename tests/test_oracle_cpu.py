@@ -201,3 +201,35 @@ def test_oracle_conv_equals_gather_gemm_scatter_on_config0():
     assert pairs == int((m[:, :c0.N] >= 0).sum())
     yt = c0.run_torch(torch, x, w, m)
     assert np.abs(y - yt).max() <= 1e-5 * max(1.0, float(np.abs(yt).max()))
+
+
+def test_dense_layouts_of_the_oracle():
+    """NCHW32 and NHWzC are index permutations of the NCHW tensor: every element of the
+    [N, C, D, H, W] scatter must be found at the documented address, padding must be zero,
+    and the int8 scatter must agree with the fp16 one on integer-valued rows."""
+    rng = np.random.default_rng(5)
+    grid, ch, n = (2, 9, 11), 24, 60
+    cells = rng.choice(grid[0] * grid[1] * grid[2], n, replace=False)
+    coords = np.zeros((n, 4), np.int32)
+    coords[:, 1], coords[:, 2], coords[:, 3] = np.unravel_index(cells, grid)
+    q = rng.integers(-128, 128, (n, ch)).astype(np.int8)
+    d8 = orc.scatter_dense_i8(q, coords, grid, 1)
+    dh = orc.scatter_dense(q.astype(np.float16), coords, grid, 1, 1.0)
+    assert np.array_equal(d8.astype(np.float16), dh)
+    perm = (2, 0, 1)
+    d8p = orc.scatter_dense_i8(q, coords, grid, 1, perm)
+    assert np.array_equal(d8p.astype(np.float16), orc.scatter_dense(q.astype(np.float16), coords,
+                                                                   grid, 1, 1.0, perm))
+    c32 = orc.dense_layout(d8, "NCHW32", ch)
+    hwzc = orc.dense_layout(d8, "NHWzC", ch)
+    assert c32.shape == (1, 2, 9, 11, 32) and hwzc.shape == (1, 9, 11, 2, ch)
+    for c in range(ch):
+        for z in range(grid[0]):
+            m = c * grid[0] + z
+            assert np.array_equal(c32[0, m // 32, :, :, m % 32], d8[0, c, z])
+            assert np.array_equal(hwzc[0, :, :, z, c], d8[0, c, z])
+    assert not c32[0, 1, :, :, 16:].any()  # 48 real channels, 16 of padding
+    view4 = d8.reshape(1, ch * grid[0], 9, 11)
+    assert np.array_equal(orc.dense_layout(view4, "NCHW32", ch), c32)
+    assert np.array_equal(orc.dense_layout(view4, "NHWzC", ch), hwzc)
+
