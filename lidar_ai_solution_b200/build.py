@@ -29,6 +29,10 @@ NVCC_FLAGS = [
 ]
 
 
+# Sources whose float arithmetic must round operation by operation (no multiply-add contraction)
+PER_FILE_FLAGS = {"centerpoint_post.cu": ("-fmad=false",)}
+
+
 def _nvcc() -> str:
     for cand in (shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
         if cand and os.path.exists(cand):
@@ -80,7 +84,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
         if force or _newer(o, [s] + headers):
             jobs.append((s, o))
     with cf.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as ex:
-        list(ex.map(lambda so: _compile(so[0], so[1], verbose), jobs))
+        list(ex.map(lambda so: _compile(so[0], so[1], verbose,
+                                        PER_FILE_FLAGS.get(os.path.basename(so[0]), ())), jobs))
     objs = [os.path.join(OBJDIR, os.path.basename(s) + ".o") for s in core_srcs]
     core = os.path.join(LIBDIR, "libspconvb.so")
     if force or jobs or not os.path.exists(core):

@@ -84,6 +84,32 @@ SYMBOLS = {
                                    _VP, _VP]),
 }
 
+class CpHead(C.Structure):
+    """spconvb_cp_head (include/spconvb_centerpoint.h)."""
+    _fields_ = [("reg", C.c_void_p), ("height", C.c_void_p), ("dim", C.c_void_p),
+                ("rot", C.c_void_p), ("vel", C.c_void_p), ("hm", C.c_void_p),
+                ("num_classes", C.c_int32), ("label_offset", C.c_int32)]
+
+
+class CpParams(C.Structure):
+    """spconvb_cp_params (include/spconvb_centerpoint.h)."""
+    _fields_ = [("H", C.c_int32), ("W", C.c_int32), ("out_size_factor", C.c_float),
+                ("voxel_size", C.c_float * 2), ("pc_range", C.c_float * 2),
+                ("score_threshold", C.c_float), ("post_center_range", C.c_float * 6),
+                ("nms_iou_threshold", C.c_float), ("max_det", C.c_int32),
+                ("nms_post_max", C.c_int32)]
+
+
+SYMBOLS.update({
+    "spconvb_cp_default_params": (None, [C.POINTER(CpParams)]),
+    "spconvb_cp_workspace_bytes": (C.c_size_t, [C.POINTER(CpParams), C.c_int32]),
+    "spconvb_cp_postprocess": (C.c_int, [C.POINTER(CpHead), C.c_int32, C.POINTER(CpParams), _VP,
+                                         C.c_size_t, _VP, _VP, _VP]),
+    "spconvb_cp_task_detections": (C.c_int, [C.POINTER(CpParams), C.c_int32, _VP, C.c_int32,
+                                             C.POINTER(_VP), C.POINTER(_VP)]),
+    "spconvb_cp_rotated_iou": (C.c_int, [_VP, _VP, C.c_int32, _VP, _VP]),
+})
+
 _LIB = None
 
 

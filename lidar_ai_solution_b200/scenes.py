@@ -118,3 +118,31 @@ def make_points(n_points: int, seed: int = 0, prange=CENTERPOINT_RANGE) -> np.nd
     p[:, 3] = rng.random(n_points)
     p[:, 4] = rng.integers(0, 11, n_points) * 0.05
     return p
+
+
+def make_centerpoint_heads(seed=0, H=180, W=180, mean_logit=-6.0, num_classes=(1, 2, 2, 1, 2, 2),
+                           objects=60):
+    """Synthetic outputs of the CenterPoint RPN + heads for one frame: per task a dict of fp16
+    arrays ``reg [2,H,W] height [1,H,W] dim [3,H,W] rot [2,H,W] vel [2,H,W] hm [C,H,W]``.
+    Heat maps are background noise around ``mean_logit`` plus ``objects`` Gaussian blobs per
+    task, so that neighbouring cells propose overlapping boxes as a trained head does."""
+    rng = np.random.default_rng(seed)
+    yy, xx = np.mgrid[0:H, 0:W].astype(np.float32)
+    heads = []
+    for classes in num_classes:
+        hm = rng.normal(mean_logit, 1.2, (classes, H, W)).astype(np.float32)
+        for _ in range(objects):
+            c = rng.integers(0, classes)
+            cy, cx = rng.uniform(0, H), rng.uniform(0, W)
+            hm[c] += rng.uniform(3.0, 9.0) * np.exp(-((yy - cy) ** 2 + (xx - cx) ** 2) / 3.0)
+        head = {
+            "hm": hm,
+            "reg": rng.uniform(0.0, 1.0, (2, H, W)),
+            "height": rng.normal(-1.0, 1.0, (1, H, W)),
+            "dim": rng.normal(0.6, 0.35, (3, H, W)),
+            "rot": rng.normal(0.0, 1.0, (2, H, W)),
+            "vel": rng.normal(0.0, 2.0, (2, H, W)),
+        }
+        heads.append({k: np.ascontiguousarray(v, np.float16) for k, v in head.items()})
+    return heads
+

@@ -26,8 +26,9 @@ KIND_F16, KIND_I8, KIND_F32 = 0, 1, 2
 def build(force: bool = False) -> str:
     """Compile ``liboracle.so`` next to its source (gcc, OpenMP)."""
     so = os.path.join(_HERE, "liboracle.so")
-    src = os.path.join(_HERE, "spconv_oracle.c")
-    if force or not os.path.exists(so) or os.path.getmtime(so) < os.path.getmtime(src):
+    srcs = [os.path.join(_HERE, f) for f in ("spconv_oracle.c", "centerpoint_post_oracle.c")]
+    if force or not os.path.exists(so) or \
+            os.path.getmtime(so) < max(os.path.getmtime(f) for f in srcs):
         subprocess.run(["make", "-C", _HERE, "-B", "liboracle.so"], check=True,
                        stdout=subprocess.DEVNULL)
     return so
@@ -39,6 +40,7 @@ def lib() -> C.CDLL:
         _LIB = C.CDLL(build())
         _LIB.orc_subm_map.restype = C.c_int64
         _LIB.orc_down_map.restype = C.c_int64
+        _LIB.orc_rotated_iou.restype = C.c_float
     return _LIB
 
 
@@ -234,3 +236,52 @@ def voxelize(points, range6, vsize, gridxyz, max_voxels=160000, max_pts=10, orde
                             order, _p(feat), _p(coords))
     m = min(nv, max_voxels)
     return feat[:m], coords[:m], int(nv)
+
+
+# ---- CenterPoint head decode + NMS (oracle/centerpoint_post_oracle.c) -------------------
+CP_DEFAULTS = dict(out_size_factor=8.0, voxel_size=(0.075, 0.075), pc_range=(-54.0, -54.0),
+                   score_threshold=0.1, post_center_range=(-61.2, -61.2, -10.0, 61.2, 61.2, 10.0),
+                   nms_iou_threshold=0.2, max_det=1000, nms_post_max=83)
+
+
+def _f(vals):
+    return (C.c_float * len(vals))(*[float(v) for v in vals])
+
+
+def centerpoint_decode(head, params=None):
+    """head: dict of fp16 arrays reg [2,H,W], height [1,H,W], dim [3,H,W], rot [2,H,W],
+    vel [2,H,W], hm [C,H,W].  Returns (detections [n, 11] float32 ranked by score, cells)."""
+    prm = dict(CP_DEFAULTS, **(params or {}))
+    t = {k: np.ascontiguousarray(head[k], np.float16) for k in ("reg", "height", "dim", "rot",
+                                                                 "vel", "hm")}
+    c_hm, h, w = t["hm"].shape
+    det = np.zeros((prm["max_det"], 11), np.float32)
+    cells = np.zeros(prm["max_det"], np.int32)
+    n = lib().orc_centerpoint_decode(
+        h, w, c_hm, _p(t["reg"]), _p(t["height"]), _p(t["dim"]), _p(t["rot"]), _p(t["vel"]),
+        _p(t["hm"]), _f(prm["post_center_range"]), C.c_float(prm["out_size_factor"]),
+        _f(prm["voxel_size"]), _f(prm["pc_range"]), C.c_float(prm["score_threshold"]),
+        int(prm["max_det"]), _p(det), _p(cells))
+    return det[:n], cells[:n]
+
+
+def centerpoint_nms(det, label_offset=0, params=None):
+    """Greedy rotated NMS over ranked detections.  Returns (boxes [k, 11] as
+    x y z w l h vx vy rt id score, kept indices, smallest |iou - threshold| evaluated)."""
+    prm = dict(CP_DEFAULTS, **(params or {}))
+    det = np.ascontiguousarray(det, np.float32)
+    out = np.zeros((max(prm["nms_post_max"], 1), 11), np.float32)
+    idx = np.zeros(max(prm["nms_post_max"], 1), np.int32)
+    margin = C.c_float(0)
+    k = lib().orc_centerpoint_nms(_p(det), len(det), C.c_float(prm["nms_iou_threshold"]),
+                                  int(prm["nms_post_max"]), int(label_offset), _p(out), _p(idx),
+                                  C.byref(margin))
+    return out[:k], idx[:k], float(margin.value)
+
+
+def rotated_iou(a, b):
+    a = np.ascontiguousarray(a, np.float32)
+    b = np.ascontiguousarray(b, np.float32)
+    return np.array([lib().orc_rotated_iou(_p(a[i]), _p(b[i])) for i in range(len(a))],
+                    np.float32)
+

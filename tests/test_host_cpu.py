@@ -22,9 +22,10 @@ def _lib():
 
 def test_library_exports_every_declared_symbol():
     cabi, lib = _lib()
-    header = open(os.path.join(ROOT, "include", "spconvb.h")).read()
+    header = open(os.path.join(ROOT, "include", "spconvb.h")).read() + \
+        open(os.path.join(ROOT, "include", "spconvb_centerpoint.h")).read()
     declared = set(re.findall(r"SPCONVB_API[^;(]*?\b(spconvb_\w+)\s*\(", header))
-    assert len(declared) >= 45
+    assert len(declared) >= 52
     from lidar_ai_solution_b200 import engine_abi
     bound = set(cabi.SYMBOLS) | set(engine_abi.SYMBOLS)
     for name in sorted(declared):
@@ -36,6 +37,15 @@ def test_library_exports_every_declared_symbol():
 
 def test_host_side_size_helpers_need_no_gpu():
     cabi, lib = _lib()
+    from lidar_ai_solution_b200 import centerpoint_post
+    cp = centerpoint_post.default_params()
+    assert (cp.H, cp.W, cp.max_det, cp.nms_post_max) == (180, 180, 1000, 83)
+    assert abs(cp.nms_iou_threshold - 0.2) < 1e-7 and abs(cp.post_center_range[3] - 61.2) < 1e-6
+    need = lib.spconvb_cp_workspace_bytes(cabi.C.byref(cp), 6)
+    assert 6 * (180 * 180 * 8 + 1000 * (44 + 32 + 128)) <= need < 4 << 20
+    assert lib.spconvb_cp_workspace_bytes(cabi.C.byref(cp), 9) == 0
+    cp.max_det = 2000
+    assert lib.spconvb_cp_workspace_bytes(cabi.C.byref(cp), 6) == 0
     assert lib.spconvb_hash_slots(120000) == 262144
     assert lib.spconvb_out_extent(41, 3, 2, 1, 1) == 21
     assert lib.spconvb_out_extent(11, 3, 2, 0, 1) == 5

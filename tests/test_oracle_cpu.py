@@ -233,3 +233,48 @@ def test_dense_layouts_of_the_oracle():
     assert np.array_equal(orc.dense_layout(view4, "NCHW32", ch), c32)
     assert np.array_equal(orc.dense_layout(view4, "NHWzC", ch), hwzc)
 
+
+def test_rotated_iou_known_answers():
+    """The bird's-eye overlap of the restated NMS against areas computed by hand."""
+    box = lambda x, y, dx, dy, a: [x, y, 0.0, dx, dy, 1.0, a]  # noqa: E731
+    a = np.array([box(0, 0, 2, 2, 0.0), box(0, 0, 2, 2, 0.0), box(0, 0, 2, 2, 0.0),
+                  box(0, 0, 2, 2, 0.0), box(0, 0, 4, 2, 0.0), box(5, 5, 2, 4, 0.3)], np.float32)
+    b = np.array([box(0, 0, 2, 2, 0.0), box(1, 0, 2, 2, 0.0), box(5, 0, 2, 2, 0.0),
+                  box(0, 0, 2, 2, np.pi / 4), box(0, 0, 2, 4, np.pi / 2), box(5, 5, 2, 4, 0.3)],
+                 np.float32)
+    got = orc.rotated_iou(a, b)
+    octagon = 8 * (np.sqrt(2) - 1)  # two unit-2 squares, one turned by 45 degrees
+    want = [1.0, 2.0 / 6.0, 0.0, octagon / (8 - octagon), 1.0, 1.0]
+    assert np.allclose(got, want, atol=2e-5), got
+
+
+def test_centerpoint_decode_and_nms_on_a_hand_made_head():
+    """Three cells above the score threshold: two overlapping boxes of one class and a distant
+    one; the decode must rank them by score and the NMS must drop the weaker of the pair."""
+    H = W = 16
+    head = {"hm": np.full((2, H, W), -9.0), "reg": np.full((2, H, W), 0.5),
+            "height": np.full((1, H, W), -1.0), "dim": np.zeros((3, H, W)),
+            "rot": np.zeros((2, H, W)), "vel": np.zeros((2, H, W))}
+    head["rot"][1] = 1.0                       # sin 0, cos 1 -> yaw 0
+    head["dim"][0] = np.log(4.0)               # 4 x 1 x 1 boxes
+    head["hm"][1, 5, 5], head["hm"][1, 5, 6], head["hm"][0, 12, 3] = 2.0, 3.0, 0.5
+    head["vel"][0, 5, 6] = 1.5
+    prm = dict(pc_range=(0.0, 0.0), post_center_range=(-100, -100, -10, 100, 100, 10))
+    det, cells = orc.centerpoint_decode(head, prm)
+    assert list(cells) == [5 * W + 6, 5 * W + 5, 12 * W + 3]
+    assert np.allclose(det[:, 10], 1 / (1 + np.exp(-np.array([3.0, 2.0, 0.5]))), rtol=1e-6)
+    assert list(det[:, 9]) == [1.0, 1.0, 0.0]
+    assert np.allclose(det[0, :9], [6.5 * 0.6, 5.5 * 0.6, -1.0, np.exp(np.float32(np.float16(np.log(4.0)))), 1.0, 1.0,
+                                   1.5, 0.0, 0.0], atol=1e-6)
+    boxes, kept, margin = orc.centerpoint_nms(det, label_offset=3, params=prm)
+    assert list(kept) == [0, 2] and margin > 1e-3
+    assert list(boxes[:, 9]) == [4.0, 3.0] and np.array_equal(boxes[:, :9], det[[0, 2], :9])
+    # a score threshold above every cell, and a centre range that excludes everything
+    assert len(orc.centerpoint_decode(head, dict(prm, score_threshold=0.99))[0]) == 0
+    assert len(orc.centerpoint_decode(head, dict(prm, post_center_range=(50, 50, -10, 60, 60, 10)))[0]) == 0
+    # more candidates than max_det: the best max_det by (score, cell) survive
+    head["hm"][0] = 1.0
+    det, cells = orc.centerpoint_decode(head, dict(prm, max_det=10))
+    assert len(det) == 10 and list(cells[:2]) == [5 * W + 6, 5 * W + 5]
+    assert list(cells[2:]) == list(range(8))
+
