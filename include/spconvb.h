@@ -339,6 +339,7 @@ typedef struct spconvb_engine spconvb_engine;
 #define SPCONVB_BUILD_KEEP_TENSORS 1u   /* no buffer reuse: every tensor stays readable */
 #define SPCONVB_BUILD_NO_FUSION 2u      /* run Add / ReLU as their own kernels */
 #define SPCONVB_BUILD_FORCE_SIMT 4u     /* CUDA-core convolution everywhere */
+#define SPCONVB_BUILD_SINGLE_STREAM 8u  /* no auxiliary stream: rulebooks and convolutions in program order */
 
 SPCONVB_API spconvb_builder* spconvb_builder_create(void);
 SPCONVB_API void spconvb_builder_destroy(spconvb_builder* b);

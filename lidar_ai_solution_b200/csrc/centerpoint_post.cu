@@ -11,7 +11,10 @@
 //   rank        one CTA per task: if more than 1024 candidates, an 8-pass radix select finds
 //               the max_det largest keys; a bitonic sort in shared memory orders them; the
 //               box parameters (exp, atan2) are evaluated for the ranked cells only
-//   mask        upper-triangular 64 x 64 tiles of pairwise rotated IoU >= threshold
+//   mask        pairwise rotated IoU >= threshold above the diagonal, in tiles of 16 x 64
+//               pairs: a reach test queues the pairs that can overlap, then the queue is
+//               spread over full warps; corners and the trigonometry of every box are
+//               prepared once by the rank kernel
 //   scan        one warp per task walks the ranking with the mask in shared memory and keeps
 //               the first nms_post_max survivors; the last CTA to finish packs all tasks'
 //               boxes into the caller's list
@@ -32,9 +35,10 @@ namespace spconvb {
 namespace {
 
 constexpr int kDet = 11;         // floats per detection
-constexpr int kBoxStride = 8;    // floats per NMS box (7 used)
+constexpr int kBoxStride = 16;   // floats per prepared NMS box (struct BoxRec)
 constexpr int kRankThreads = 1024;
 constexpr int kMaskWords = 16;   // 64-bit words per mask row: 1024 / 64
+constexpr int kScanStagedRows = 320;  // mask rows the scan keeps in shared memory (40 KB)
 
 struct TaskBuffers {
   uint32_t* n_cand;
@@ -42,7 +46,7 @@ struct TaskBuffers {
   uint32_t* n_kept;
   unsigned long long* cand;  // [H*W]
   float* det;                // [max_det][11]
-  float* box;                // [max_det][8]
+  float* box;                // [max_det][16], BoxRec
   unsigned long long* mask;  // [max_det][16]
   float* kept;               // [post_max][11]
 };
@@ -135,6 +139,147 @@ __global__ void cp_candidates_kernel(const PostArgs a) {
   a.buf[task].cand[slot] = key;  // at most one key per cell, so slot < H*W
 }
 
+// ------------------------------------------------------------------ rotated overlap
+struct Pt { float x, y; };
+
+// A box as the overlap test wants it: centre, extents, the rotation by -angle used by the
+// corner-inside-box test, and the four corners turned by +angle about the centre.
+struct BoxRec {
+  float x, y, dx, dy;
+  float cos_neg, sin_neg;
+  Pt corner[4];
+  float angle, reach;  // reach: half the diagonal, the farthest any point of the box is from its centre
+};
+static_assert(sizeof(BoxRec) == sizeof(float) * kBoxStride, "BoxRec layout");
+
+__device__ __forceinline__ void prepare_box(const float* box, BoxRec& r) {
+  r.x = box[0]; r.y = box[1]; r.dx = box[3]; r.dy = box[4];
+  r.angle = box[6];
+  r.reach = 0.5f * sqrtf(box[3] * box[3] + box[4] * box[4]);
+  r.cos_neg = cosf(-box[6]);
+  r.sin_neg = sinf(-box[6]);
+  const float hx = box[3] / 2, hy = box[4] / 2;
+  const float x1 = box[0] - hx, y1 = box[1] - hy, x2 = box[0] + hx, y2 = box[1] + hy;
+  const float co = cosf(box[6]), si = sinf(box[6]);
+  const float rx[4] = {x1, x2, x2, x1}, ry[4] = {y1, y1, y2, y2};
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    r.corner[k].x = (rx[k] - box[0]) * co + (ry[k] - box[1]) * (-si) + box[0];
+    r.corner[k].y = (rx[k] - box[0]) * si + (ry[k] - box[1]) * co + box[1];
+  }
+}
+
+__device__ __forceinline__ float cross3(Pt p1, Pt p2, Pt p0) {
+  return (p1.x - p0.x) * (p2.y - p0.y) - (p2.x - p0.x) * (p1.y - p0.y);
+}
+
+__device__ __forceinline__ bool inside_with_margin(const BoxRec& box, Pt p) {
+  const float margin = 1e-2f;
+  const float rx = (p.x - box.x) * box.cos_neg + (p.y - box.y) * (-box.sin_neg);
+  const float ry = (p.x - box.x) * box.sin_neg + (p.y - box.y) * box.cos_neg;
+  return fabsf(rx) < box.dx / 2 + margin && fabsf(ry) < box.dy / 2 + margin;
+}
+
+__device__ __forceinline__ bool segments_cross(Pt p1, Pt p0, Pt q1, Pt q0, Pt& ans) {
+  if (!(fminf(p0.x, p1.x) <= fmaxf(q0.x, q1.x) && fminf(q0.x, q1.x) <= fmaxf(p0.x, p1.x) &&
+        fminf(p0.y, p1.y) <= fmaxf(q0.y, q1.y) && fminf(q0.y, q1.y) <= fmaxf(p0.y, p1.y)))
+    return false;
+  const float s1 = cross3(q0, p1, p0);
+  const float s2 = cross3(p1, q1, p0);
+  const float s3 = cross3(p0, q1, q0);
+  const float s4 = cross3(q1, p1, q0);
+  if (!(s1 * s2 > 0 && s3 * s4 > 0)) return false;
+  const float s5 = cross3(q1, p1, p0);
+  if ((double)fabsf(s5 - s1) > 1e-8) {
+    ans.x = (s5 * q0.x - s1 * q1.x) / (s5 - s1);
+    ans.y = (s5 * q0.y - s1 * q1.y) / (s5 - s1);
+  } else {
+    const float a0 = p0.y - p1.y, b0 = p1.x - p0.x, c0 = p0.x * p1.y - p1.x * p0.y;
+    const float a1 = q0.y - q1.y, b1 = q1.x - q0.x, c1 = q0.x * q1.y - q1.x * q0.y;
+    const float D = a0 * b1 - a1 * b0;
+    ans.x = (b0 * c1 - b1 * c0) / D;
+    ans.y = (a1 * c0 - a0 * c1) / D;
+  }
+  return true;
+}
+
+__device__ float rotated_iou(const BoxRec& A, const BoxRec& B) {
+  // Boxes farther apart than their reaches (plus far more than the 1e-2 margin of the corner
+  // test and any rounding) share no edge crossing and no corner: the full computation below
+  // would find no point and return 0 as well.
+  {
+    const float ddx = A.x - B.x, ddy = A.y - B.y, far = A.reach + B.reach + 0.1f;
+    if (ddx * ddx + ddy * ddy > far * far) return 0.f;
+  }
+  Pt pts[16];
+  float ang[16];
+  int cnt = 0;
+  Pt centre = {0.f, 0.f};
+  for (int i = 0; i < 4; ++i)
+    for (int j = 0; j < 4; ++j) {
+      Pt x;
+      if (segments_cross(A.corner[(i + 1) & 3], A.corner[i], B.corner[(j + 1) & 3], B.corner[j], x)) {
+        centre.x = centre.x + x.x;
+        centre.y = centre.y + x.y;
+        pts[cnt++] = x;
+      }
+    }
+  for (int k = 0; k < 4; ++k) {
+    if (inside_with_margin(A, B.corner[k])) {
+      centre.x = centre.x + B.corner[k].x;
+      centre.y = centre.y + B.corner[k].y;
+      pts[cnt++] = B.corner[k];
+    }
+    if (inside_with_margin(B, A.corner[k])) {
+      centre.x = centre.x + A.corner[k].x;
+      centre.y = centre.y + A.corner[k].y;
+      pts[cnt++] = A.corner[k];
+    }
+  }
+  if (cnt == 0) return 0.f;
+  centre.x /= (float)cnt;
+  centre.y /= (float)cnt;
+  // stable ascending order of the polar angle about the centre
+  for (int k = 0; k < cnt; ++k) ang[k] = atan2f(pts[k].y - centre.y, pts[k].x - centre.x);
+  for (int k = 1; k < cnt; ++k) {
+    const Pt p = pts[k];
+    const float ak = ang[k];
+    int j = k - 1;
+    while (j >= 0 && ang[j] > ak) {
+      pts[j + 1] = pts[j];
+      ang[j + 1] = ang[j];
+      --j;
+    }
+    pts[j + 1] = p;
+    ang[j + 1] = ak;
+  }
+  float area = 0.f;
+  for (int k = 0; k + 1 < cnt; ++k) {
+    const float ax = pts[k].x - pts[0].x, ay = pts[k].y - pts[0].y;
+    const float bx = pts[k + 1].x - pts[0].x, by = pts[k + 1].y - pts[0].y;
+    area += ax * by - ay * bx;
+  }
+  const float overlap = fabsf(area) / 2.0f;
+  const float sa = A.dx * A.dy, sb = B.dx * B.dy;
+  return overlap / fmaxf(sa + sb - overlap, 1e-8f);
+}
+
+__global__ void rotated_iou_pairs_kernel(const float* a, const float* b, int n, float* iou) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  BoxRec A, B;
+  prepare_box(a + (size_t)i * 7, A);
+  prepare_box(b + (size_t)i * 7, B);
+  iou[i] = rotated_iou(A, B);
+}
+
+__device__ __forceinline__ void load_box(const float* p, BoxRec& r) {
+  float4* d = (float4*)&r;
+  const float4* s4 = (const float4*)p;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) d[k] = s4[k];
+}
+
 // ------------------------------------------------------------------ rank
 __global__ void __launch_bounds__(kRankThreads) cp_rank_kernel(const PostArgs a) {
   const int task = blockIdx.x;
@@ -161,20 +306,41 @@ __global__ void __launch_bounds__(kRankThreads) cp_rank_kernel(const PostArgs a)
       __syncthreads();
       const unsigned long long prefix = s_prefix;
       const unsigned long long hi = shift == 56 ? 0ull : (~0ull << (shift + 8));
-      for (uint32_t i = tid; i < n; i += kRankThreads) {
-        const unsigned long long k = b.cand[i];
-        if (((k ^ prefix) & hi) == 0ull) atomicAdd(&hist[(uint32_t)(k >> shift) & 255u], 1u);
+      for (uint32_t base = 0; base < n; base += kRankThreads) {
+        // keys of one score share their upper bytes: lanes with the same digit add once
+        const uint32_t i = base + tid;
+        const unsigned long long k = i < n ? b.cand[i] : 0ull;
+        const bool live = i < n && ((k ^ prefix) & hi) == 0ull;
+        const uint32_t digit = live ? ((uint32_t)(k >> shift) & 255u) : 256u;
+        const uint32_t peers = __match_any_sync(0xffffffffu, digit);
+        if (live && (tid & 31) == __ffs(peers) - 1) atomicAdd(&hist[digit], (uint32_t)__popc(peers));
       }
       __syncthreads();
-      if (tid == 0) {
-        uint32_t need = s_need, above = 0u;
-        int d = 255;
-        for (; d > 0; --d) {
-          if (above + hist[d] >= need) break;
-          above += hist[d];
+      if (tid < 32) {
+        // lane l owns bins 8l..8l+7; the digit is the highest bin whose count, together with
+        // everything above it, reaches what is still needed
+        uint32_t mine[8], sum = 0u;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) { mine[k] = hist[tid * 8 + k]; sum += mine[k]; }
+        uint32_t incl = sum;  // becomes the count in this lane's bins and in all higher lanes
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const uint32_t v = __shfl_down_sync(0xffffffffu, incl, d);
+          if (tid + d < 32) incl += v;
         }
-        s_need = need - above;
-        s_prefix = prefix | ((unsigned long long)d << shift);
+        const uint32_t above = incl - sum;
+        const uint32_t need = s_need;
+        const bool here = above < need && incl >= need;  // exactly one lane
+        if (here) {
+          uint32_t acc = above;
+          int k = 7;
+          for (; k > 0; --k) {
+            if (acc + mine[k] >= need) break;
+            acc += mine[k];
+          }
+          s_need = need - acc;
+          s_prefix = prefix | ((unsigned long long)(tid * 8 + k) << shift);
+        }
       }
       __syncthreads();
     }
@@ -190,10 +356,13 @@ __global__ void __launch_bounds__(kRankThreads) cp_rank_kernel(const PostArgs a)
   }
 
   // bitonic sort, descending (padding keys are 0 and end up last)
-  for (int size = 2; size <= kRankThreads; size <<= 1) {
+  const int filled = n <= (uint32_t)kRankThreads ? (int)n : (int)K;  // keys beyond are zero padding
+  int sort_n = 32;
+  while (sort_n < filled) sort_n <<= 1;
+  for (int size = 2; size <= sort_n; size <<= 1) {
     for (int stride = size >> 1; stride > 0; stride >>= 1) {
       const int partner = tid ^ stride;
-      if (partner > tid) {
+      if (partner > tid && partner < sort_n) {
         const unsigned long long x = keys[tid], y = keys[partner];
         const bool descending = (tid & size) == 0;
         if ((x < y) == descending) { keys[tid] = y; keys[partner] = x; }
@@ -223,163 +392,83 @@ __global__ void __launch_bounds__(kRankThreads) cp_rank_kernel(const PostArgs a)
   d[0] = xs; d[1] = ys; d[2] = zs; d[3] = dx; d[4] = dy; d[5] = dz;
   d[6] = vx; d[7] = vy; d[8] = rs; d[9] = (float)label; d[10] = score;
   // the box NMS sees: length and width swapped, yaw turned into the lidar frame
-  float* q = b.box + (size_t)tid * kBoxStride;
-  q[0] = xs; q[1] = ys; q[2] = zs; q[3] = dy; q[4] = dx; q[5] = dz;
-  q[6] = (float)(-(double)rs - 3.141592653 * 0.5);
-  q[7] = 0.f;
-}
-
-// ------------------------------------------------------------------ rotated overlap
-struct Pt { float x, y; };
-
-__device__ __forceinline__ float cross3(Pt p1, Pt p2, Pt p0) {
-  return (p1.x - p0.x) * (p2.y - p0.y) - (p2.x - p0.x) * (p1.y - p0.y);
-}
-
-__device__ __forceinline__ bool inside_with_margin(const float* box, Pt p) {
-  const float margin = 1e-2f;
-  const float c = cosf(-box[6]), s = sinf(-box[6]);
-  const float rx = (p.x - box[0]) * c + (p.y - box[1]) * (-s);
-  const float ry = (p.x - box[0]) * s + (p.y - box[1]) * c;
-  return fabsf(rx) < box[3] / 2 + margin && fabsf(ry) < box[4] / 2 + margin;
-}
-
-__device__ __forceinline__ bool segments_cross(Pt p1, Pt p0, Pt q1, Pt q0, Pt& ans) {
-  if (!(fminf(p0.x, p1.x) <= fmaxf(q0.x, q1.x) && fminf(q0.x, q1.x) <= fmaxf(p0.x, p1.x) &&
-        fminf(p0.y, p1.y) <= fmaxf(q0.y, q1.y) && fminf(q0.y, q1.y) <= fmaxf(p0.y, p1.y)))
-    return false;
-  const float s1 = cross3(q0, p1, p0);
-  const float s2 = cross3(p1, q1, p0);
-  const float s3 = cross3(p0, q1, q0);
-  const float s4 = cross3(q1, p1, q0);
-  if (!(s1 * s2 > 0 && s3 * s4 > 0)) return false;
-  const float s5 = cross3(q1, p1, p0);
-  if ((double)fabsf(s5 - s1) > 1e-8) {
-    ans.x = (s5 * q0.x - s1 * q1.x) / (s5 - s1);
-    ans.y = (s5 * q0.y - s1 * q1.y) / (s5 - s1);
-  } else {
-    const float a0 = p0.y - p1.y, b0 = p1.x - p0.x, c0 = p0.x * p1.y - p1.x * p0.y;
-    const float a1 = q0.y - q1.y, b1 = q1.x - q0.x, c1 = q0.x * q1.y - q1.x * q0.y;
-    const float D = a0 * b1 - a1 * b0;
-    ans.x = (b0 * c1 - b1 * c0) / D;
-    ans.y = (a1 * c0 - a0 * c1) / D;
-  }
-  return true;
-}
-
-__device__ __forceinline__ void box_corners(const float* box, Pt* c5) {
-  const float hx = box[3] / 2, hy = box[4] / 2;
-  const float x1 = box[0] - hx, y1 = box[1] - hy, x2 = box[0] + hx, y2 = box[1] + hy;
-  const float co = cosf(box[6]), si = sinf(box[6]);
-  const float rx[4] = {x1, x2, x2, x1}, ry[4] = {y1, y1, y2, y2};
-#pragma unroll
-  for (int k = 0; k < 4; ++k) {
-    c5[k].x = (rx[k] - box[0]) * co + (ry[k] - box[1]) * (-si) + box[0];
-    c5[k].y = (rx[k] - box[0]) * si + (ry[k] - box[1]) * co + box[1];
-  }
-  c5[4] = c5[0];
-}
-
-__device__ float rotated_iou(const float* box_a, const float* box_b) {
-  Pt ca[5], cb[5], pts[16];
-  float ang[16];
-  box_corners(box_a, ca);
-  box_corners(box_b, cb);
-  int cnt = 0;
-  Pt centre = {0.f, 0.f};
-  for (int i = 0; i < 4; ++i)
-    for (int j = 0; j < 4; ++j) {
-      Pt x;
-      if (segments_cross(ca[i + 1], ca[i], cb[j + 1], cb[j], x)) {
-        centre.x = centre.x + x.x;
-        centre.y = centre.y + x.y;
-        pts[cnt++] = x;
-      }
-    }
-  for (int k = 0; k < 4; ++k) {
-    if (inside_with_margin(box_a, cb[k])) {
-      centre.x = centre.x + cb[k].x;
-      centre.y = centre.y + cb[k].y;
-      pts[cnt++] = cb[k];
-    }
-    if (inside_with_margin(box_b, ca[k])) {
-      centre.x = centre.x + ca[k].x;
-      centre.y = centre.y + ca[k].y;
-      pts[cnt++] = ca[k];
-    }
-  }
-  if (cnt == 0) return 0.f;
-  centre.x /= (float)cnt;
-  centre.y /= (float)cnt;
-  // stable ascending order of the polar angle about the centre
-  for (int k = 0; k < cnt; ++k) ang[k] = atan2f(pts[k].y - centre.y, pts[k].x - centre.x);
-  for (int k = 1; k < cnt; ++k) {
-    const Pt p = pts[k];
-    const float ak = ang[k];
-    int j = k - 1;
-    while (j >= 0 && ang[j] > ak) {
-      pts[j + 1] = pts[j];
-      ang[j + 1] = ang[j];
-      --j;
-    }
-    pts[j + 1] = p;
-    ang[j + 1] = ak;
-  }
-  float area = 0.f;
-  for (int k = 0; k + 1 < cnt; ++k) {
-    const float ax = pts[k].x - pts[0].x, ay = pts[k].y - pts[0].y;
-    const float bx = pts[k + 1].x - pts[0].x, by = pts[k + 1].y - pts[0].y;
-    area += ax * by - ay * bx;
-  }
-  const float overlap = fabsf(area) / 2.0f;
-  const float sa = box_a[3] * box_a[4], sb = box_b[3] * box_b[4];
-  return overlap / fmaxf(sa + sb - overlap, 1e-8f);
-}
-
-__global__ void rotated_iou_pairs_kernel(const float* a, const float* b, int n, float* iou) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < n) iou[i] = rotated_iou(a + (size_t)i * 7, b + (size_t)i * 7);
+  const float nms_box[7] = {xs, ys, zs, dy, dx, dz, (float)(-(double)rs - 3.141592653 * 0.5)};
+  prepare_box(nms_box, *(BoxRec*)(b.box + (size_t)tid * kBoxStride));
 }
 
 // ------------------------------------------------------------------ mask
-__global__ void __launch_bounds__(64) cp_mask_kernel(const PostArgs a) {
-  const int task = blockIdx.z;
+constexpr int kMaskRows = 16;          // ranked boxes per tile; divides 64, so a tile's rows share a word
+constexpr int kMaskCtasPerTask = 148;
+constexpr int kMaskThreads = 128;
+
+// One tile = 16 rows x 64 partners.  Pass 1: every thread tests 8 pairs for reach (three floats
+// per box, staged in shared memory) and queues the few that can overlap.  Pass 2: the queued
+// pairs are spread over the threads one by one, so the long overlap computation runs with full
+// warps instead of one lane in 32.
+__global__ void __launch_bounds__(kMaskThreads) cp_mask_kernel(const PostArgs a) {
+  const int task = blockIdx.y;
   const TaskBuffers& b = a.buf[task];
-  const int row_blk = blockIdx.y, col_blk = blockIdx.x;
   const int m = (int)*b.n_det;
-  if (row_blk > col_blk || row_blk * 64 >= m || col_blk * 64 >= m) return;
   const int tid = threadIdx.x;
-  const int rows = min(m - row_blk * 64, 64), cols = min(m - col_blk * 64, 64);
-  __shared__ float col_box[64 * kBoxStride];
-  if (tid < cols) {
-    const float4* src = (const float4*)(b.box + (size_t)(col_blk * 64 + tid) * kBoxStride);
-    ((float4*)col_box)[tid * 2] = src[0];
-    ((float4*)col_box)[tid * 2 + 1] = src[1];
+  __shared__ float col_x[64], col_y[64], col_r[64], row_x[kMaskRows], row_y[kMaskRows], row_r[kMaskRows];
+  __shared__ unsigned long long words[kMaskRows];
+  __shared__ uint16_t queue[kMaskRows * 64];
+  __shared__ uint32_t queued;
+  const int col_blocks = (m + 63) / 64, row_groups = (m + kMaskRows - 1) / kMaskRows;
+  for (int tile = blockIdx.x; tile < col_blocks * row_groups; tile += gridDim.x) {
+    const int row0 = (tile / col_blocks) * kMaskRows, col0 = (tile % col_blocks) * 64;
+    if (col0 / 64 < row0 / 64) continue;  // left of the diagonal: never read
+    __syncthreads();                      // the previous tile's shared state is no longer needed
+    if (tid < 64) {
+      const BoxRec* r = (const BoxRec*)(b.box + (size_t)min(col0 + tid, m - 1) * kBoxStride);
+      col_x[tid] = r->x; col_y[tid] = r->y; col_r[tid] = r->reach;
+    } else if (tid < 64 + kMaskRows) {
+      const int k = tid - 64;
+      const BoxRec* r = (const BoxRec*)(b.box + (size_t)min(row0 + k, m - 1) * kBoxStride);
+      row_x[k] = r->x; row_y[k] = r->y; row_r[k] = r->reach;
+      words[k] = 0ull;
+    } else if (tid == 64 + kMaskRows) {
+      queued = 0u;
+    }
+    __syncthreads();
+    for (int pair = tid; pair < kMaskRows * 64; pair += kMaskThreads) {
+      const int r = pair >> 6, c = pair & 63;
+      const int i = row0 + r, j = col0 + c;
+      if (i >= m || j >= m || j <= i) continue;
+      const float ddx = row_x[r] - col_x[c], ddy = row_y[r] - col_y[c];
+      const float far = row_r[r] + col_r[c] + 0.1f;
+      if (ddx * ddx + ddy * ddy > far * far) continue;  // the same test rotated_iou starts with
+      queue[atomicAdd(&queued, 1u)] = (uint16_t)pair;
+    }
+    __syncthreads();
+    const uint32_t n_pairs = queued;
+    for (uint32_t q = tid; q < n_pairs; q += kMaskThreads) {
+      const int pair = queue[q], r = pair >> 6, c = pair & 63;
+      BoxRec A, B;
+      load_box(b.box + (size_t)(row0 + r) * kBoxStride, A);
+      load_box(b.box + (size_t)(col0 + c) * kBoxStride, B);
+      if (rotated_iou(A, B) >= a.p.nms_iou_threshold) atomicOr(&words[r], 1ull << c);
+    }
+    __syncthreads();
+    if (tid < kMaskRows && row0 + tid < m)
+      b.mask[(size_t)(row0 + tid) * kMaskWords + col0 / 64] = words[tid];
   }
-  __syncthreads();
-  if (tid >= rows) return;
-  const int i = row_blk * 64 + tid;
-  float mine[kBoxStride];
-  {
-    const float4* src = (const float4*)(b.box + (size_t)i * kBoxStride);
-    *(float4*)&mine[0] = src[0];
-    *(float4*)&mine[4] = src[1];
-  }
-  unsigned long long bits = 0ull;
-  for (int j = (row_blk == col_blk ? tid + 1 : 0); j < cols; ++j)
-    if (rotated_iou(mine, col_box + j * kBoxStride) >= a.p.nms_iou_threshold) bits |= 1ull << j;
-  b.mask[(size_t)i * kMaskWords + col_blk] = bits;
 }
 
 // ------------------------------------------------------------------ scan
 __global__ void __launch_bounds__(512) cp_scan_kernel(const PostArgs a) {
-  extern __shared__ unsigned long long s_mask[];  // [m][16]
+  __shared__ unsigned long long s_mask[kScanStagedRows * kMaskWords];
   __shared__ bool s_last;
+  __shared__ int s_kept[kRankThreads];
+  __shared__ uint32_t s_nkept;
   const int task = blockIdx.x;
   const TaskBuffers& b = a.buf[task];
   const int m = (int)*b.n_det;
   const int words = (m + 63) / 64;
-  for (int i = threadIdx.x; i < m * kMaskWords; i += blockDim.x) {
+  // The walk usually ends (nms_post_max survivors) within the first few hundred boxes: those
+  // rows are staged in shared memory, later ones are read from global memory when needed.
+  const int staged = min(m, kScanStagedRows);
+  for (int i = threadIdx.x; i < staged * kMaskWords; i += blockDim.x) {
     const int row = i / kMaskWords, wd = i % kMaskWords;
     // words left of the diagonal tile and right of the last box are never written
     s_mask[i] = (wd >= row / 64 && wd < words) ? b.mask[i] : 0ull;
@@ -389,19 +478,30 @@ __global__ void __launch_bounds__(512) cp_scan_kernel(const PostArgs a) {
     const int lane = threadIdx.x;
     unsigned long long removed = 0ull;  // lane w holds word w of the removed set
     uint32_t kept = 0;
-    for (int i = 0; i < m; ++i) {
+    // boxes after the first nms_post_max survivors cannot reach the output
+    for (int i = 0; i < m && kept < (uint32_t)a.p.nms_post_max; ++i) {
       const unsigned long long wd = __shfl_sync(0xffffffffu, removed, i >> 6);
       if ((wd >> (i & 63)) & 1ull) continue;
-      if (kept < (uint32_t)a.p.nms_post_max && lane < kDet) {
-        float v = b.det[(size_t)i * kDet + lane];
-        if (lane == 9) v = (float)(a.head[task].label_offset + (int)v);
-        b.kept[(size_t)kept * kDet + lane] = v;
-      }
+      if (lane == 0) s_kept[kept] = i;
       ++kept;
-      if (lane < kMaskWords) removed |= s_mask[i * kMaskWords + lane];
+      if (lane < kMaskWords) {
+        if (i < staged) removed |= s_mask[i * kMaskWords + lane];
+        else if (lane >= (i >> 6) && lane < words) removed |= b.mask[(size_t)i * kMaskWords + lane];
+      }
     }
-    if (lane == 0) *b.n_kept = min(kept, (uint32_t)a.p.nms_post_max);
+    if (lane == 0) {
+      s_nkept = kept;
+      *b.n_kept = kept;
+    }
   }
+  __syncthreads();
+  for (uint32_t e = threadIdx.x; e < s_nkept * kDet; e += blockDim.x) {
+    const uint32_t k = e / kDet, f = e % kDet;
+    float v = b.det[(size_t)s_kept[k] * kDet + f];
+    if (f == 9) v = (float)(a.head[task].label_offset + (int)v);
+    b.kept[e] = v;
+  }
+  __threadfence();  // every thread's rows are visible device-wide before the ticket is taken
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence();
@@ -474,20 +574,15 @@ int spconvb_cp_postprocess(const spconvb_cp_head* heads, int32_t num_tasks,
   a.out_count = out_count;
   bind_buffers(l, workspace, num_tasks, a);
   cudaStream_t st = (cudaStream_t)stream;
-  const size_t scan_smem = sizeof(unsigned long long) * kMaskWords * (size_t)p->max_det;
-  SPCONVB_CUDA_TRY(cudaFuncSetAttribute(
-      cp_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-      (int)(sizeof(unsigned long long) * kMaskWords * kRankThreads)));
   SPCONVB_CUDA_TRY(cudaMemsetAsync(workspace, 0, l.counters_bytes, st));
   const int HW = p->H * p->W;
   cp_candidates_kernel<<<dim3((HW + 255) / 256, num_tasks), 256, 0, st>>>(a);
   SPCONVB_LAUNCH_CHECK();
   cp_rank_kernel<<<num_tasks, kRankThreads, 0, st>>>(a);
   SPCONVB_LAUNCH_CHECK();
-  const int blocks = (p->max_det + 63) / 64;
-  cp_mask_kernel<<<dim3(blocks, blocks, num_tasks), 64, 0, st>>>(a);
+  cp_mask_kernel<<<dim3(kMaskCtasPerTask, num_tasks), kMaskThreads, 0, st>>>(a);
   SPCONVB_LAUNCH_CHECK();
-  cp_scan_kernel<<<num_tasks, 512, scan_smem, st>>>(a);
+  cp_scan_kernel<<<num_tasks, 512, 0, st>>>(a);
   SPCONVB_LAUNCH_CHECK();
   return SPCONVB_OK;
 }

@@ -64,6 +64,10 @@ int Builder::push(GNode&& n, const std::string& out_name) {
 // ------------------------------------------------------------------- engine
 Engine::~Engine() {
   free_prepared();
+  for (cudaEvent_t e : rule_ev_)
+    if (e) cudaEventDestroy(e);
+  if (fork_ev_) cudaEventDestroy(fork_ev_);
+  if (aux_) cudaStreamDestroy(aux_);
   for (auto& w : weights) {
     cudaFree(w.plain);
     cudaFree(w.packed);
@@ -686,6 +690,11 @@ int Engine::collect_absmax(float* out, cudaStream_t st) {
 
 static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
+static bool is_rulebook_step(const Step& s) {
+  return s.kind == Step::HASH || s.kind == Step::SUBM_MAP || s.kind == Step::DOWN_MAP ||
+         s.kind == Step::INV_MAP;
+}
+
 int Engine::prepare(const int32_t grid[3], int batch) {
   if (prepared_ && same3(grid_, grid) && batch_ == batch) return SPCONVB_OK;
   cudaDeviceSynchronize();
@@ -798,14 +807,24 @@ int Engine::prepare(const int32_t grid[3], int batch) {
     t.data = slots[pick].ptr;
   }
   if (cudaDeviceSynchronize() != cudaSuccess) return SPCONVB_E_NOMEM;
+  if (!(flags & SPCONVB_BUILD_SINGLE_STREAM) && !aux_) {
+    bool ok = cudaStreamCreateWithFlags(&aux_, cudaStreamNonBlocking) == cudaSuccess &&
+              cudaEventCreateWithFlags(&fork_ev_, cudaEventDisableTiming) == cudaSuccess;
+    rule_ev_.assign(steps.size(), nullptr);
+    for (size_t i = 0; ok && i < steps.size(); ++i)
+      if (is_rulebook_step(steps[i]))
+        ok = cudaEventCreateWithFlags(&rule_ev_[i], cudaEventDisableTiming) == cudaSuccess;
+    if (!ok) return SPCONVB_E_NOMEM;
+  }
   prepared_ = true;
   return SPCONVB_OK;
 }
 
 int Engine::forward(const void* features, const int32_t* indices, uint32_t cap_rows,
                     uint32_t n_host, const uint32_t* n_dev, const int32_t grid[3], int batch,
-                    cudaStream_t st, const Profile* prof) {
+                    cudaStream_t caller_stream, const Profile* prof) {
   if (input_rt_ < 0 || !features || !indices || !grid) return SPCONVB_E_ARG;
+  cudaStream_t st = caller_stream;  // the stream run_step launches on; switched for rulebook steps
   int rc = prepare(grid, batch);
   if (rc != SPCONVB_OK) return rc;
   CoordSet& in = coordsets[rt[input_rt_].cs];
@@ -927,9 +946,37 @@ int Engine::forward(const void* features, const int32_t* indices, uint32_t cap_r
     if (cudaEventCreate(&ev0) != cudaSuccess || cudaEventCreate(&ev1) != cudaSuccess)
       return SPCONVB_E_NOMEM;
   }
+  // Fork: the rulebook steps go to the auxiliary stream in their original order; a feature
+  // step waits for the last rulebook step that precedes it in the program, which covers its
+  // rulebook, its coordinate set and its row count.  Nothing a rulebook step reads is written
+  // by a feature step.  The caller's stream joins the auxiliary one before returning, so the
+  // whole call remains one unit of work on that stream (and one capturable region).
+  const bool fork = !prof && aux_ != nullptr;
+  int last_rule = -1, waited = -1;
+  if (fork) {
+    if (cudaEventRecord(fork_ev_, caller_stream) != cudaSuccess ||
+        cudaStreamWaitEvent(aux_, fork_ev_, 0) != cudaSuccess)
+      return SPCONVB_E_DEVICE;
+  }
   for (size_t si = 0; si < steps.size(); ++si) {
     const Step& s = steps[si];
-    if (!prof) {
+    if (fork) {
+      if (is_rulebook_step(s)) {
+        st = aux_;
+        rc = run_step(s);
+        st = caller_stream;
+        if (rc == SPCONVB_OK && cudaEventRecord(rule_ev_[si], aux_) != cudaSuccess)
+          rc = SPCONVB_E_DEVICE;
+        last_rule = (int)si;
+      } else {
+        if (last_rule > waited) {
+          if (cudaStreamWaitEvent(caller_stream, rule_ev_[last_rule], 0) != cudaSuccess)
+            rc = SPCONVB_E_DEVICE;
+          waited = last_rule;
+        }
+        if (rc == SPCONVB_OK) rc = run_step(s);
+      }
+    } else if (!prof) {
       rc = run_step(s);
     } else {
       // Per-step device time: rulebook steps change state and run once; the
@@ -958,6 +1005,11 @@ int Engine::forward(const void* features, const int32_t* indices, uint32_t cap_r
       log_msg(LOG_ERROR, "step '%s' failed: %s", s.name.c_str(), spconvb_error_string(rc));
       break;
     }
+  }
+  if (fork) {  // join, also after a failed step, so that the auxiliary stream never outlives the call
+    if (cudaEventRecord(fork_ev_, aux_) != cudaSuccess ||
+        cudaStreamWaitEvent(caller_stream, fork_ev_, 0) != cudaSuccess)
+      rc = rc == SPCONVB_OK ? SPCONVB_E_DEVICE : rc;
   }
   if (prof) {
     cudaEventDestroy(ev0);

@@ -173,6 +173,11 @@ class Engine {
   int32_t grid_[3] = {0, 0, 0};
   int batch_ = 0;
   std::vector<void*> allocations_;
+  // Rulebook steps depend on coordinates only: they run ahead on this stream while the
+  // caller's stream does the convolutions, joined by one event per rulebook step.
+  cudaStream_t aux_ = nullptr;
+  cudaEvent_t fork_ev_ = nullptr;
+  std::vector<cudaEvent_t> rule_ev_;
   void* zero_arena_ = nullptr;
   size_t zero_bytes_ = 0;
   uint32_t* counts_ = nullptr;

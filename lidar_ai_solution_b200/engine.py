@@ -14,7 +14,7 @@ import numpy as np
 import torch
 
 from . import cabi, engine_abi, onnx_writer
-from .engine_abi import (BUILD_FORCE_SIMT, BUILD_KEEP_TENSORS, BUILD_NO_FUSION,  # noqa: F401
+from .engine_abi import (BUILD_FORCE_SIMT, BUILD_KEEP_TENSORS, BUILD_NO_FUSION, BUILD_SINGLE_STREAM,  # noqa: F401
                          PRECISION_FP16, PRECISION_INT8)
 
 

@@ -11,7 +11,7 @@ _U16P = C.POINTER(C.c_uint16)
 _CP = C.c_char_p
 
 PRECISION_FP16, PRECISION_INT8 = 1, 2
-BUILD_KEEP_TENSORS, BUILD_NO_FUSION, BUILD_FORCE_SIMT = 1, 2, 4
+BUILD_KEEP_TENSORS, BUILD_NO_FUSION, BUILD_FORCE_SIMT, BUILD_SINGLE_STREAM = 1, 2, 4, 8
 
 
 class TensorView(C.Structure):

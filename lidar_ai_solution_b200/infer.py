@@ -44,7 +44,7 @@ def parse_args(argv=None):
     _flag(ap, "int8", "false", "main precision int8 (wins over fp16)")
     _flag(ap, "sortmask", "false", "accepted, ignored")
     _flag(ap, "blackwell", "false", "accepted, ignored (always sm_100a kernels)")
-    _flag(ap, "auxiliary_stream", "false", "accepted, ignored")
+    _flag(ap, "auxiliary_stream", "true", "build the rulebooks on a second stream inside the engine")
     _flag(ap, "cudagraph", "false", "capture the forward in a CUDA graph and replay it")
     ap.add_argument("--fixed_points", type=int, default=10000,
                     help="fixed launch size of all kernels (with cudagraph or dds)")
@@ -111,7 +111,8 @@ def run_task(task, cudagraph, dds, fixed_points, profiling, stress=False, quiet=
     dev = torch.device("cuda", torch.cuda.current_device())
     n = len(task.features)
     use_fixed = fixed_points if (cudagraph or dds) else 0
-    eng = engine.Engine.from_onnx(task.onnx, task.precision, 0, use_fixed, dev)
+    flags = 0 if a.auxiliary_stream else engine.BUILD_SINGLE_STREAM
+    eng = engine.Engine.from_onnx(task.onnx, task.precision, flags, use_fixed, dev)
     stream = torch.cuda.Stream(device=dev)  # "Please avoid using the default stream"
     f = torch.from_numpy(task.features).to(dev)
     c = torch.from_numpy(task.indices).to(dev)

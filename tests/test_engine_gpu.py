@@ -274,6 +274,57 @@ def test_dds_forward_and_cuda_graph_replay():
             assert float(got.abs().max()) == 0.0
 
 
+def test_auxiliary_stream_changes_no_result():
+    """The engine builds the rulebooks on its own second stream by default.  Every tensor must
+    equal the single-stream build's, eagerly and through a replayed CUDA graph, frame after
+    frame on one engine."""
+    eng = _engine_mod()
+    frames = [_frame(n, seed=s) for n, s in ((9000, 5), (4000, 6), (12000, 7))]
+    model = _quantized("centerpoint", *frames[0], seed=5)
+    ref = eng.Engine.from_model(model, eng.PRECISION_INT8, eng.BUILD_SINGLE_STREAM | eng.BUILD_KEEP_TENSORS)
+    two = eng.Engine.from_model(model, eng.PRECISION_INT8, eng.BUILD_KEEP_TENSORS)
+    fast = eng.Engine.from_model(model, eng.PRECISION_INT8, 0)
+    cap = 12000
+    f_buf = torch.zeros((cap, 5), dtype=torch.float16, device="cuda")
+    c_buf = torch.zeros((cap, 4), dtype=torch.int32, device="cuda")
+    n_dev = torch.zeros(1, dtype=torch.int32, device="cuda")
+    stream = torch.cuda.Stream()
+    graph = None
+    for feats, coords in frames + frames[:1]:
+        n = len(feats)
+        ref.forward(_dev(feats), _dev(coords), GRID)
+        two.forward(_dev(feats), _dev(coords), GRID)
+        torch.cuda.synchronize()
+        assert ref.status()[0] == 0 and two.status()[0] == 0
+        want = ref.output(0).cpu().numpy()
+        assert np.array_equal(two.output(0).cpu().numpy().view(np.uint16), want.view(np.uint16))
+        compared = 0
+        for tid in models.tensor_ids(model)[1:]:
+            try:
+                a, b = ref.tensor(tid), two.tensor(tid)
+            except RuntimeError:  # fused into its consumer: no buffer of its own
+                continue
+            compared += 1
+            assert a["n"] == b["n"]
+            assert torch.equal(a["features"][:a["n"]], b["features"][:b["n"]]), tid
+        assert compared >= 10
+        f_buf[:n].copy_(_dev(feats))
+        c_buf[:n].copy_(_dev(coords))
+        n_dev.fill_(n)
+        torch.cuda.synchronize()
+        with torch.cuda.stream(stream):
+            if graph is None:
+                fast.forward_dds(f_buf, c_buf, n_dev, GRID, stream=stream)
+                stream.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    fast.forward_dds(f_buf, c_buf, n_dev, GRID, stream=stream)
+            graph.replay()
+        torch.cuda.synchronize()
+        assert fast.status()[0] == 0
+        assert np.array_equal(fast.output(0).cpu().numpy().view(np.uint16), want.view(np.uint16))
+
+
 def test_single_layer_sparse_output_and_bounds():
     eng = _engine_mod()
     feats, coords = _frame(5000, seed=5)
