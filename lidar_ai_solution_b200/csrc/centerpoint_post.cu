@@ -457,7 +457,7 @@ __global__ void __launch_bounds__(kMaskThreads) cp_mask_kernel(const PostArgs a)
 
 // ------------------------------------------------------------------ scan
 __global__ void __launch_bounds__(512) cp_scan_kernel(const PostArgs a) {
-  __shared__ unsigned long long s_mask[kScanStagedRows * kMaskWords];
+  __shared__ __align__(16) unsigned long long s_mask[kScanStagedRows * kMaskWords];
   __shared__ bool s_last;
   __shared__ int s_kept[kRankThreads];
   __shared__ uint32_t s_nkept;
@@ -468,25 +468,44 @@ __global__ void __launch_bounds__(512) cp_scan_kernel(const PostArgs a) {
   // The walk usually ends (nms_post_max survivors) within the first few hundred boxes: those
   // rows are staged in shared memory, later ones are read from global memory when needed.
   const int staged = min(m, kScanStagedRows);
-  for (int i = threadIdx.x; i < staged * kMaskWords; i += blockDim.x) {
-    const int row = i / kMaskWords, wd = i % kMaskWords;
-    // words left of the diagonal tile and right of the last box are never written
-    s_mask[i] = (wd >= row / 64 && wd < words) ? b.mask[i] : 0ull;
+  {
+    // 16-byte loads issued back to back; words left of the diagonal tile and right of the last
+    // box were never written and are zeroed here
+    const ulonglong2* src = (const ulonglong2*)b.mask;
+    ulonglong2* dst = (ulonglong2*)s_mask;
+    const int vecs = staged * (kMaskWords / 2);
+#pragma unroll 5
+    for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
+      ulonglong2 x = src[v];
+      const int row = v / (kMaskWords / 2), wd = (v % (kMaskWords / 2)) * 2;
+      if (wd < row / 64 || wd >= words) x.x = 0ull;
+      if (wd + 1 < row / 64 || wd + 1 >= words) x.y = 0ull;
+      dst[v] = x;
+    }
   }
   __syncthreads();
   if (threadIdx.x < 32) {
     const int lane = threadIdx.x;
     unsigned long long removed = 0ull;  // lane w holds word w of the removed set
     uint32_t kept = 0;
-    // boxes after the first nms_post_max survivors cannot reach the output
-    for (int i = 0; i < m && kept < (uint32_t)a.p.nms_post_max; ++i) {
-      const unsigned long long wd = __shfl_sync(0xffffffffu, removed, i >> 6);
-      if ((wd >> (i & 63)) & 1ull) continue;
-      if (lane == 0) s_kept[kept] = i;
-      ++kept;
-      if (lane < kMaskWords) {
-        if (i < staged) removed |= s_mask[i * kMaskWords + lane];
-        else if (lane >= (i >> 6) && lane < words) removed |= b.mask[(size_t)i * kMaskWords + lane];
+    // Word by word: the lowest ranked box of the word that nobody has removed survives, its
+    // mask row joins the removed set, and so on; removed boxes cost nothing.  Boxes after the
+    // first nms_post_max survivors cannot reach the output.
+    for (int w = 0; w < words && kept < (uint32_t)a.p.nms_post_max; ++w) {
+      const unsigned long long valid =
+          (w == words - 1 && (m & 63)) ? ((1ull << (m & 63)) - 1ull) : ~0ull;
+      while (kept < (uint32_t)a.p.nms_post_max) {
+        const unsigned long long alive = ~__shfl_sync(0xffffffffu, removed, w) & valid;
+        if (alive == 0ull) break;
+        const int bit = __ffsll((long long)alive) - 1;
+        const int i = w * 64 + bit;
+        if (lane == 0) s_kept[kept] = i;
+        ++kept;
+        if (lane == w) removed |= 1ull << bit;  // done with this box
+        if (lane < kMaskWords) {
+          if (i < staged) removed |= s_mask[i * kMaskWords + lane];
+          else if (lane >= w && lane < words) removed |= b.mask[(size_t)i * kMaskWords + lane];
+        }
       }
     }
     if (lane == 0) {
@@ -511,12 +530,15 @@ __global__ void __launch_bounds__(512) cp_scan_kernel(const PostArgs a) {
   if (!s_last) return;
   __threadfence();
   // the last task to finish packs every task's boxes into the caller's list, in task order
-  uint32_t base = 0;
-  for (int t = 0; t < a.num_tasks; ++t) {
-    const uint32_t k = __ldcg(a.buf[t].n_kept);
-    for (uint32_t i = threadIdx.x; i < k * kDet; i += blockDim.x)
+  uint32_t count[SPCONVB_CP_MAX_TASKS], base = 0;
+#pragma unroll
+  for (int t = 0; t < SPCONVB_CP_MAX_TASKS; ++t)
+    count[t] = t < a.num_tasks ? __ldcg(a.buf[t].n_kept) : 0u;
+#pragma unroll
+  for (int t = 0; t < SPCONVB_CP_MAX_TASKS; ++t) {
+    for (uint32_t i = threadIdx.x; i < count[t] * kDet; i += blockDim.x)
       a.out_boxes[(size_t)base * kDet + i] = __ldcg(a.buf[t].kept + i);
-    base += k;
+    base += count[t];
   }
   if (threadIdx.x == 0) *a.out_count = base;
 }
