@@ -117,6 +117,31 @@ def test_empty_and_single_task_frames():
     assert np.allclose(got, boxes, rtol=RTOL, atol=1e-6)
 
 
+@pytest.mark.parametrize("max_det", [64, 1000])
+def test_tied_scores_rank_by_cell_index(max_det):
+    """Heat maps with only five distinct logits: thousands of cells tie exactly, all pass the
+    score filter, and the radix select has to cut inside a run of equal scores.  The ranking is
+    then decided by the cell index, on the device as in the restatement."""
+    post = _post()
+    rng = np.random.default_rng(2)
+    H, W = 64, 80
+    heads = scenes.make_centerpoint_heads(2, H=H, W=W, num_classes=(2,), objects=0)
+    heads[0]["hm"] = rng.choice(np.array([-1.0, -0.5, 0.0, 0.5, 2.0], np.float16), (2, H, W))
+    prm = dict(max_det=max_det, nms_post_max=min(50, max_det), pc_range=(-20.0, -20.0),
+               post_center_range=(-100, -100, -10, 100, 100, 10))
+    det, cells = orc.centerpoint_decode(heads[0], prm)
+    boxes, kept, margin = orc.centerpoint_nms(det, 2, prm)
+    assert len(det) == max_det and margin > 1e-4
+    assert len(np.unique(det[:, 10])) <= 3 and np.all(np.diff(cells[det[:, 10] == det[0, 10]]) > 0)
+    pp = post.PostProcess(post.default_params(H, W, **prm), num_tasks=1)
+    pp.run(_dev_heads(heads), label_offsets=(2,))
+    d = pp.task_detections(0).cpu().numpy()
+    assert np.array_equal(d[:, :3], det[:, :3]) and np.array_equal(d[:, 9:], det[:, 9:])
+    got = pp.result().cpu().numpy()
+    assert np.array_equal(got[:, 9], boxes[:, 9]) and np.array_equal(got[:, :3], boxes[:, :3])
+    assert np.allclose(got, boxes, rtol=RTOL, atol=1e-6)
+
+
 def test_postprocess_is_capturable_and_repeatable():
     """No host synchronisation inside: the call records into a CUDA graph; replays on new head
     values give the restatement's answer each time."""
