@@ -1,4 +1,4 @@
-"""ctypes front-end of the CPU oracle (``oracle/spconv_oracle.c``).
+"""ctypes front-end of the CPU oracle (``oracle/spconv_oracle.c``, ``oracle/centerpoint_post_oracle.c``).
 
 TEST INFRASTRUCTURE ONLY: imported by the test-suite, the smoke check and the
 benchmark's ``cpu_baseline`` / ``--impl reference`` legs.  The shipped package
