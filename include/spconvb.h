@@ -164,7 +164,10 @@ SPCONVB_API int spconvb_down_map(const int32_t* in_coords, const uint32_t* n_in_
  *    with that device current).  Make that first call outside stream capture.
  *  - All calls on a device share the one scratch area.  It is cleared at the
  *    start of every call, so back-to-back calls on one stream are fine; calls
- *    that can overlap on the GPU (different streams, no dependency) race. */
+ *    that can overlap on the GPU (different streams, no dependency) race.
+ *  - The looked-up address is kept for the life of the process: do not call
+ *    cudaDeviceReset (or otherwise destroy the device's primary context) between
+ *    calls. */
 #define SPCONVB_STATIC_SCRATCH_BYTES (4u << 20)
 SPCONVB_API int spconvb_down_map_static(const int32_t* in_coords, const uint32_t* n_in_ptr,
                                         uint32_t cap_in, uint32_t launch_rows,
@@ -207,6 +210,11 @@ typedef struct spconvb_conv_params {
                            * from the w-th K chunk of every CTA on, so the consumer's wait must
                            * run out; the launch then ends with SPCONVB_ST_TIMEOUT in the status
                            * block, its output undefined, the context and TMEM usable */
+  /* Optional hint for the tensor-core kernel's L2 prefetch of input rows: the device-side
+   * row count of `in` and the rows its buffer holds.  NULL / 0: input rows are not
+   * prefetched (results are the same either way). */
+  const uint32_t* n_in_ptr;
+  uint32_t cap_in;
 } spconvb_conv_params;
 
 /* Bytes of the packed device image of a weight tensor for the tensor-core path. */
@@ -235,7 +243,10 @@ SPCONVB_API int spconvb_conv_forward(const spconvb_conv_params* p, const void* i
 
 /* ------------------------------------------------------------ elementwise
  * Add / Add&ReLU / ReLU (EngineBuilder::push_add, push_relu, engine.hpp:100-112),
- * precision changes between layers, and channel padding of the input. */
+ * precision changes between layers, and channel padding of the input.
+ * In this group and in the two ScatterDense calls `launch_rows` is also the row capacity of
+ * the buffers: rows [0, min(*n_ptr, launch_rows)) are processed, so a device-side count
+ * larger than the buffers never makes a kernel read or write past them. */
 
 SPCONVB_API int spconvb_add(const void* a, int32_t a_kind, float a_scale, const void* b,
                             int32_t b_kind, float b_scale, int32_t channels,
@@ -445,6 +456,15 @@ SPCONVB_API int spconvb_engine_output(const spconvb_engine* e, int i, void** dat
 SPCONVB_API int spconvb_engine_output_layout(const spconvb_engine* e, int i, int32_t* layout,
                                              int64_t physical_shape[8], int32_t* ndim,
                                              size_t* bytes);
+
+/* Rows of sparse output i (SparseDTensor::indices() / grid_size() of an engine output,
+ * engine.hpp:38-50): its coordinates [cap][4] (the caller's own index buffer when the output
+ * lives on the input's rows: then *coords is NULL and *on_input_rows is 1), the device word
+ * holding the row count (rows beyond it are undefined), the capacity and the grid.  Any
+ * out-pointer may be NULL.  Dense outputs: SPCONVB_E_ARG. */
+SPCONVB_API int spconvb_engine_output_rows(const spconvb_engine* e, int i, int32_t** coords,
+                                           uint32_t** n_ptr, uint32_t* cap, int32_t grid[3],
+                                           int32_t* on_input_rows);
 
 /* Any tensor by name (needs SPCONVB_BUILD_KEEP_TENSORS for intermediates):
  * features pointer, element kind, channels as stored, int8 scale, coordinates

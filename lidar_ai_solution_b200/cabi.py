@@ -10,7 +10,8 @@ import ctypes as C
 import os
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "lib", "libspconvb.so")
+# SPCONVB_LIB: path of another build of the same library (to compare two builds)
+LIB_PATH = os.environ.get("SPCONVB_LIB") or os.path.join(_PKG, "lib", "libspconvb.so")
 
 OK = 0
 F16, I8 = 0, 1
@@ -28,6 +29,7 @@ class ConvParams(C.Structure):
         ("res", C.c_void_p), ("res_kind", C.c_int32), ("res_scale", C.c_float),
         ("mid_kind", C.c_int32), ("mid_inv_scale", C.c_float), ("mid_scale", C.c_float),
         ("res_relu", C.c_int32), ("force_simt", C.c_int32), ("wait_test", C.c_int32),
+        ("n_in_ptr", C.c_void_p), ("cap_in", C.c_uint32),
     ]
 
 

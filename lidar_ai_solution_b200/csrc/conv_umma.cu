@@ -1,5 +1,7 @@
 // Tensor-core convolution, host side: the supported shapes, the pre-swizzled weight
 // image the kernel streams, argument checks and the launch.
+#include <stdlib.h>
+
 #include "umma_common.cuh"
 
 namespace spconvb {
@@ -7,7 +9,7 @@ namespace spconvb {
 using namespace umma_detail;
 
 int conv_umma_kernel_launch(const UmmaArgs& a, bool int8, int rb, int cout, uint32_t launch_rows,
-                       cudaStream_t st);
+                            size_t smem, cudaStream_t st);
 
 bool conv_umma_supported(int compute, int cin, int cout) {
   const int rb = row_bytes(compute, cin);
@@ -43,6 +45,76 @@ int conv_umma_pack(int compute, int cin, int cout, int kvol, const void* w, void
   return SPCONVB_OK;
 }
 
+// Launch configuration: copies of the weights along the accumulator rows, residency of the
+// weights, depth of the row-stage ring, and how far the L2 prefetch runs ahead.
+struct UmmaConfig {
+  int w_rep;
+  int w_resident;
+  int nstages;
+  int prefetch;
+  size_t smem;
+};
+
+// Tuning overrides, read once: SPCONVB_CONV_M (64 or 128 accumulator rows), SPCONVB_CONV_RESIDENT
+// (0 / 1), SPCONVB_CONV_STAGES (2..6), SPCONVB_CONV_PREFETCH (tiles ahead, 0 = off).  Unset or
+// out of range: the built-in choice.  Results do not depend on any of them.
+static int env_int(const char* name, int fallback) {
+  const char* v = getenv(name);
+  if (!v || !*v) return fallback;
+  return atoi(v);
+}
+
+static bool config_fits(int rb, int cout, int nchunk, int rep, int resident, int stages,
+                        size_t* smem) {
+  *smem = umma_smem_bytes(rb, cout, nchunk, rep, resident, stages);
+  return *smem <= 232448;
+}
+
+// Residency removes the weight chunk from every stage (as much L2 traffic and shared-memory
+// writing as half the gathered rows), so it is preferred whenever it leaves at least three
+// stages.  128 accumulator rows (the most copies) come first: with 64 rows half the lanes of
+// every epilogue warp carry nothing, and the epilogue of a tile must not outlast the next
+// tile's main loop.
+static UmmaConfig choose_config(int rb, int cout, int kvol) {
+  static const int force_m = env_int("SPCONVB_CONV_M", 0);
+  static const int force_res = env_int("SPCONVB_CONV_RESIDENT", -1);
+  static const int force_stages = env_int("SPCONVB_CONV_STAGES", 0);
+  static const int prefetch = env_int("SPCONVB_CONV_PREFETCH", 3);
+  const int nchunk = (kvol * rb + kChunk - 1) / kChunk;
+  const int full = 128 / cout, half = cout <= 64 ? 64 / cout : 0;
+  auto best_stages = [&](int rep, int resident) {
+    size_t smem;
+    int st = 0;
+    for (int n = 2; n <= kMaxStages; ++n)
+      if (config_fits(rb, cout, nchunk, rep, resident, n, &smem)) st = n;
+    if (force_stages >= 2 && force_stages <= st) st = force_stages;
+    return st;
+  };
+  struct Cand { int rep, resident, need; };
+  Cand order[4] = {{full, 1, 3}, {half, 1, 3}, {full, 0, 2}, {half, 0, 2}};
+  UmmaConfig c{};
+  for (const Cand& o : order) {
+    if (o.rep < 1) continue;
+    if (force_m == 64 && o.rep != half) continue;
+    if (force_m == 128 && o.rep != full) continue;
+    if (force_res >= 0 && o.resident != force_res) continue;
+    const int st = best_stages(o.rep, o.resident);
+    if (st < o.need) continue;
+    c.w_rep = o.rep;
+    c.w_resident = o.resident;
+    c.nstages = st;
+    break;
+  }
+  if (c.nstages == 0) {  // the overrides excluded everything: fall back to streaming, full rows
+    c.w_rep = full;
+    c.w_resident = 0;
+    c.nstages = best_stages(full, 0);
+  }
+  c.prefetch = prefetch < 0 ? 0 : (prefetch > 8 ? 8 : prefetch);
+  c.smem = umma_smem_bytes(rb, cout, nchunk, c.w_rep, c.w_resident, c.nstages);
+  return c;
+}
+
 int conv_umma_launch(const spconvb_conv_params& p, const void* in, const int32_t* map,
                      uint32_t cap, const uint32_t* n_out_ptr, uint32_t launch_rows,
                      const void* w_packed, const float* scale, const float* bias, void* out,
@@ -63,25 +135,19 @@ int conv_umma_launch(const spconvb_conv_params& p, const void* in, const int32_t
   a.res = (const uint8_t*)p.res;
   a.out = (uint8_t*)out;
   a.status = status;
+  a.n_in_ptr = p.cap_in ? p.n_in_ptr : nullptr;
+  a.cap_in = p.cap_in;
   a.kvol = p.kvol;
   a.wait_test = p.wait_test;
-  // Copies of the weights along the accumulator lanes, and residency.  Every copy lets
-  // more epilogue warps share a tile, but a streamed stage always moves 128 weight rows,
-  // as much L2 traffic as the gathered rows cost.  So: the most copies with which all
-  // chunks of the layer still fit in the 64 KB the weight stages occupy, loaded once;
-  // if not even one copy fits, stream with full replication.
-  {
-    const int rbytes = row_bytes(p.compute, p.cin);
-    const size_t nchunk = ((size_t)p.kvol * rbytes + kChunk - 1) / kChunk;
-    const int full = 128 / p.cout;
-    int rep = full;
-    while (rep >= 1 && nchunk * (size_t)rep * p.cout * kChunk > 65536) rep /= 2;
-    a.w_resident = rep >= 1;
-    a.w_rep = rep >= 1 ? rep : full;
-  }
-  a.ep = make_epilogue(p);
   const int rb = row_bytes(p.compute, p.cin);
-  return conv_umma_kernel_launch(a, p.compute == SPCONVB_I8, rb, p.cout, launch_rows, st);
+  const UmmaConfig c = choose_config(rb, p.cout, p.kvol);
+  if (c.nstages < 2) return SPCONVB_E_UNSUPPORTED;
+  a.w_rep = c.w_rep;
+  a.w_resident = c.w_resident;
+  a.nstages = c.nstages;
+  a.prefetch = c.prefetch;
+  a.ep = make_epilogue(p);
+  return conv_umma_kernel_launch(a, p.compute == SPCONVB_I8, rb, p.cout, launch_rows, c.smem, st);
 }
 
 }  // namespace spconvb

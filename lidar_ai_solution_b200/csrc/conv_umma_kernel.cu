@@ -6,64 +6,74 @@
 // is a GEMM between the weights [Cout x K] and a matrix [rows x K], K = kvol *
 // Cin, that does not exist in memory: its row o is the concatenation of the
 // feature rows of o's neighbours (zeros where a neighbour is absent).  A
-// tcgen05.mma with 128 accumulator lanes takes the same time whether it is 16
-// or 256 columns wide, so the voxel rows are put on the wide side: the weights
-// are the M operand (128 accumulator lanes = output channels), a tile of 256
-// voxel rows is the N operand, and the accumulator in TMEM is the transposed
-// output tile  D[channel][row].  With fewer than 128 output channels the weight
-// chunk is copied several times into the M operand, so that more lane quadrants
-// hold all channels and the epilogue warps of different quadrants can share the
-// rows of the tile between them instead of idling.  When all chunks of the layer
-// (times the copies) fit in 64 KB they are loaded once and stay in shared memory;
-// otherwise a chunk is streamed with every stage.  Streaming costs as much L2
-// traffic as the gathers themselves (128 weight rows per 256 gathered rows), so
-// the host side trades copies for residency.  The kernel is persistent (one CTA
-// per SM) and warp-specialised:
+// tcgen05.mma takes the same time whether its accumulator has 64 or 128 rows, and
+// its time grows with its columns, so the voxel rows are put on the wide side: the
+// weights are the M operand (64 or 128 accumulator rows = output channels, copied
+// w_rep times when Cout is smaller), a tile of up to 256 voxel rows is the N
+// operand, and the accumulator in TMEM is the transposed output tile
+// D[channel][row].  Copies of the weights let more epilogue warps share a tile.
+// When all chunks of the layer (times the copies) fit beside the row stages they
+// are loaded once and stay in shared memory; otherwise a chunk is streamed with
+// every stage.  The host side (conv_umma.cu) picks copies, residency and the depth
+// of the stage ring from the shared-memory budget.  The kernel is persistent (one
+// CTA per SM) and warp-specialised:
 //
-//   warps 0-7   epilogue: warp w reads lanes 32*(w%4).. (its channels) and
-//               Cout columns (its share of the tile's rows) of the accumulator with
-//               tcgen05.ld, applies dequant + bias + activation (+ residual
-//               add) + requant with per-lane scale and bias, transposes 4x4
-//               blocks inside lane quads with two shuffles, and stores 4 (int8)
-//               or 8 (fp16) contiguous bytes of one output row per lane
+//   warps 0-7   epilogue: warp w reads its lane quadrant (its channels) and its
+//               share of the tile's rows from the accumulator with tcgen05.ld,
+//               applies dequant + bias + activation (+ residual add) + requant
+//               with per-lane scale and bias, transposes 4x4 blocks inside lane
+//               quads with two shuffles, and stores 4 (int8) or 8 (fp16)
+//               contiguous bytes of one output row per lane
 //   warp  8     allocates TMEM; one lane issues tcgen05.mma (kind::i8 with int32
 //               accumulators or kind::f16 with fp32 accumulators)
-//   warps 9-16  producers: each warp owns 32 rows of the tile.  It prefetches
-//               their neighbour indices one tile ahead into registers and
-//               stages them in its own piece of shared memory (no CTA-wide
-//               synchronisation), gathers the neighbour rows with 16-byte
-//               cp.async (8 lanes per row, so a row is one contiguous request;
-//               zero-fill for missing neighbours) straight into the
-//               128-byte-swizzled K-major layout the MMA reads, fences the
-//               generic-proxy writes for the async proxy and arrives once per
-//               warp; one thread also streams the pre-swizzled weight chunk
-//               with one bulk async copy
+//   warps 9-16  producers: each warp owns 32 rows of the tile.  Neighbour indices
+//               travel chunk by chunk: 4-byte cp.async copies, two chunks ahead,
+//               straight into a small per-warp ring in shared memory (no register
+//               staging, nothing to stall on), from where the gathering threads
+//               take eight at a time.
+//               Rows are gathered with 16-byte cp.async (8 lanes per row, so a row
+//               is one contiguous request; zero-fill for missing neighbours)
+//               straight into the 128-byte-swizzled K-major layout the MMA reads.
+//               A producer never waits for its copies: every thread lets them
+//               arrive on the stage's mbarrier when they land, so all free stages
+//               of the ring are in flight.  One thread also streams the
+//               pre-swizzled weight chunk with one bulk async copy, and a few
+//               lanes ask L2 (bulk prefetch) for the map lines, input rows and
+//               residual rows of the tile the CTA will reach some rounds later,
+//               so that the gathers find them in L2 instead of HBM.
 //
 // K is walked in chunks of 128 bytes (one swizzle atom per row): a chunk is 8
 // taps of a 16-byte row, ..., 1 tap of a 128-byte row, or half a 256-byte row.
-// Stages cycle through a 4-deep ring guarded by mbarriers; the accumulator
-// is double-buffered in TMEM (2 x 256 columns) so the epilogue of tile t
-// overlaps the MMAs of tile t+1.
+// The accumulator is double-buffered in TMEM (2 x 256 columns) so the epilogue of
+// tile t overlaps the MMAs of tile t+1.
 //
 // Every wait is bounded: a wait that runs out sets SPCONVB_ST_TIMEOUT in the
 // status block, raises a CTA-wide abort flag and all roles leave their loops,
 // drain their copies and free TMEM.
 #include "umma_common.cuh"
 
+// Per-role cycle accounting, compiled in only with -DSPCONVB_CONV_PROFILE (a measurement
+// build, never the shipped one): one lane of a producer warp, the MMA thread and one
+// epilogue lane add up the clock cycles they spend in each part of their loops, per CTA;
+// spconvb_debug_conv_profile() copies the table out.  In that build a negative
+// spconvb_conv_params.wait_test -f switches work off: f & 1 no gather copies, f & 2 no MMAs,
+// f & 4 no index copies, f & 8 one "stage full" arrival per producer warp instead of one per
+// thread (4 and 8 also switch the gather copies off: they would be wrong with them).
+#ifdef SPCONVB_CONV_PROFILE
+#define PROF(...) __VA_ARGS__
+#else
+#define PROF(...)
+#endif
+
 namespace spconvb {
 
 using namespace umma_detail;
 
+PROF(__device__ unsigned long long g_conv_profile[148][16];)
+
 namespace {
 
 constexpr int kTileRows = 256;  // most voxel rows per tile: the largest N of the MMA
-constexpr int kMmaM = 128;      // accumulator lanes: output channels, padded
-// Stage ring: as deep as shared memory allows next to the index staging area (a stage is
-// 32 KB of rows + 16 KB of weights).  A producer signals a stage "full" kLag chunks after
-// issuing its copies; the other kStages - kLag stages are slack for the round trip
-// through the MMA.
-constexpr int kStages = 4;
-constexpr int kLag = 1;
 constexpr int kRowsBytes = kTileRows * kChunk;  // gathered rows of one stage
 constexpr int kEpiWarps = 8;
 constexpr int kMmaWarp = 8;
@@ -71,14 +81,16 @@ constexpr int kProdWarp0 = 9;
 constexpr int kProdThreads = 256;
 constexpr int kCtaThreads = 32 * kProdWarp0 + kProdThreads;
 constexpr uint32_t kTmemCols = 2 * kTileRows;
+constexpr int kIdxTapStride = 36;  // words between taps in the index ring (32 rows + padding
+                                   // that spreads the taps of a 16-byte read over all banks)
+constexpr size_t kMaxSmem = 232448;  // 227 KB: the most dynamic shared memory of a CTA
 
 // 32-bit instruction descriptor: [4,6) D format (1 = f32, 2 = s32), [7,10) A
 // format, [10,13) B format (f16 kind: 0 = f16; i8 kind: 1 = signed), bits 15/16
-// A/B major (0 = K), [17,23) N>>3, [24,29) M>>4.
+// A/B major (0 = K), [17,23) N>>3, [24,29) M>>4.  M and N are added per launch.
 template <bool INT8>
 __device__ __forceinline__ constexpr uint32_t make_idesc() {
-  return (INT8 ? ((2u << 4) | (1u << 7) | (1u << 10)) : (1u << 4)) |
-         ((uint32_t)(kMmaM >> 4) << 24);  // N is added per launch: (tile rows >> 3) << 17
+  return INT8 ? ((2u << 4) | (1u << 7) | (1u << 10)) : (1u << 4);
 }
 
 // Transposes inside a quad of lanes (lane = 4g + j): they turn "my channel for a
@@ -125,36 +137,38 @@ __device__ __forceinline__ void quad_transpose_h16(uint32_t& w0, uint32_t& w1, u
   if (hi) w0 = other; else w1 = other;
 }
 
-constexpr size_t umma_smem_bytes() {
-  return 1024 + (size_t)kStages * (kRowsBytes + kMmaM * kChunk) +
-         (size_t)kMaxTaps * kTileRows * sizeof(int32_t) + 256;
-}
-
 // ------------------------------------------------------------------- kernel
 template <bool INT8, int RB, int COUT>
 __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArgs a) {
-  constexpr int kWBytes = kMmaM * kChunk;      // weight stage when streaming: 128 rows
-  constexpr int kWChunk = COUT * kChunk;       // one copy of a chunk, as packed in global memory
   constexpr int OPC = RB <= kChunk ? kChunk / RB : 1;   // taps per chunk
   constexpr int SPO = RB <= kChunk ? RB / 16 : 8;       // 16-byte segments per tap per chunk
   constexpr int CPT = RB <= kChunk ? 1 : RB / kChunk;   // chunks per tap
+  constexpr int kIdxSlot = OPC * kIdxTapStride;         // words of one ring slot of one warp
 
-  // Shared memory: the weight stages (128 rows each: the replicated chunk), the
-  // gathered-row stages, the producers' neighbour indices of the current tile, the
-  // barriers.
+  const int kbytes = a.kvol * RB;
+  const int nchunk = (kbytes + kChunk - 1) / kChunk;
+  const int last_ksteps = ((kbytes - (nchunk - 1) * kChunk) + 31) / 32;
+  const uint32_t w_rep = (uint32_t)a.w_rep;
+  const uint32_t m_rows = w_rep * COUT;            // accumulator rows of the MMA: 64 or 128
+  const bool w_resident = a.w_resident != 0;
+  const uint32_t w_chunk_smem = m_rows * kChunk;   // bytes of one chunk with its copies
+  const uint32_t nst = (uint32_t)a.nstages;
+
+  // Shared memory: the weights (all chunks, or one per stage), the gathered-row stages,
+  // the producers' index rings, the barriers.
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
   uint8_t* sW = smem;
-  uint8_t* sR = sW + kStages * kWBytes;
-  int32_t* sIdx = (int32_t*)(sR + kStages * kRowsBytes);  // [kMaxTaps][kTileRows]
-  uint64_t* bars = (uint64_t*)(sIdx + kMaxTaps * kTileRows);
-  uint32_t* tmem_holder = (uint32_t*)(bars + 2 * kStages + 5);
+  uint8_t* sR = sW + (w_resident ? (uint32_t)nchunk : nst) * w_chunk_smem;
+  int32_t* sIdx = (int32_t*)(sR + nst * kRowsBytes);
+  uint64_t* bars = (uint64_t*)((uint8_t*)sIdx + umma_idx_bytes(RB));
+  uint32_t* tmem_holder = (uint32_t*)(bars + 2 * kMaxStages + 5);
   volatile uint32_t* abort_flag = tmem_holder + 1;
 
   const uint32_t bar_full = smem_u32(bars);
-  const uint32_t bar_empty = bar_full + 8 * kStages;
-  const uint32_t bar_tfull = bar_empty + 8 * kStages;
+  const uint32_t bar_empty = bar_full + 8 * kMaxStages;
+  const uint32_t bar_tfull = bar_empty + 8 * kMaxStages;
   const uint32_t bar_tempty = bar_tfull + 16;
   const uint32_t bar_w = bar_tempty + 16;  // resident weights have landed
 
@@ -162,8 +176,9 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
   const uint32_t lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(bar_full + 8 * s, kProdThreads / 32 + 1);
+    for (int s = 0; s < kMaxStages; ++s) {
+      mbar_init(bar_full + 8 * s, kProdThreads + 1);  // every producer thread + the weights
+      PROF(if (a.wait_test < 0 && ((-a.wait_test) & 8)) mbar_init(bar_full + 8 * s, 9);)
       mbar_init(bar_empty + 8 * s, 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -197,127 +212,167 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
   const uint32_t tile_rows =
       min((uint32_t)kTileRows, max(32u, ((per_cta + rounds - 1) / rounds + 31u) & ~31u));
   const uint32_t ntiles = (n_out + tile_rows - 1) / tile_rows;
-  const int kbytes = a.kvol * RB;
-  const int nchunk = (kbytes + kChunk - 1) / kChunk;
-  const int last_ksteps = ((kbytes - (nchunk - 1) * kChunk) + 31) / 32;
-  const uint32_t w_rep = (uint32_t)a.w_rep;
-  const bool w_resident = a.w_resident != 0;
-  const uint32_t w_chunk_smem = w_rep * kWChunk;  // bytes of one chunk with its copies
 
   if (warp >= kProdWarp0) {
     // ------------------------------------------------------------ producers
     // A chunk of the row tile is 256 rows x 8 segments of 16 bytes = 2048 copies,
-    // 8 per producer thread.  Producer warp w owns rows 32w..32w+31; lanes run over
-    // the segments first (8 lanes per row), so the lanes that read the same
-    // neighbour row ask for one contiguous piece of it and a warp instruction
-    // touches 4..32 cache lines, not always 32.  The code is branch-free (missing
-    // neighbours are zero-filled copies) so the index loads, address arithmetic and
-    // copies of the 8 items overlap.
+    // 8 per producer thread.  Producer warp w owns rows 32w..32w+31; a thread copies
+    // segment `seg` of rows 32w + 8 slot + i, i = 0..7 (8 lanes per row, so the lanes
+    // that read the same neighbour row ask for one contiguous piece of it).  The code
+    // is branch-free (missing neighbours are zero-filled copies) so the address
+    // arithmetic and the copies of the 8 items overlap.
     const uint32_t pw = (uint32_t)warp - kProdWarp0;
     const uint32_t r = threadIdx.x - kProdWarp0 * 32;  // thread 0 also copies the weights
     const uint32_t seg = lane & 7u;        // 16-byte segment of the chunk this thread copies
-    const uint32_t slot = lane >> 3;       // rows 32w + slot + 4i, i = 0..7
+    const uint32_t slot = lane >> 3;       // its 8 rows of the warp's 32
     // row R of the tile lives at (R / 8) * 1024 + (R % 8) * 128, its segments XOR-ed
-    // with R % 8; R % 8 is slot for even i and slot + 4 for odd i
-    const uint32_t dst_even = pw * 4096u + slot * 128u + ((seg ^ slot) << 4);
-    const uint32_t dst_odd = pw * 4096u + (slot + 4u) * 128u + ((seg ^ (slot + 4u)) << 4);
+    // with R % 8; here R / 8 = 4 pw + slot and R % 8 = i
+    const uint32_t dst_base = (pw * 4u + slot) * 1024u;
     // tap (within the chunk) and byte offset (within the neighbour row) of `seg`
     const uint32_t seg_tap = RB <= kChunk ? seg / SPO : 0u;
     const uint32_t seg_byte = RB <= kChunk ? (seg % SPO) * 16u : seg * 16u;
-    // Neighbour indices: lane l fetches the taps of row 32w + l of the next tile
-    // into registers while the current tile is gathered, and stores them in the
-    // warp's own staging area when the warp is done with the current tile.  The area
-    // is [tap][slot][i] for row slot + 4i, so that the 8 indices a gathering thread
-    // needs for a tap are two 16-byte loads.
-    int32_t* widx = sIdx + pw * (kMaxTaps * 32);
-    auto fetch_indices = [&](uint32_t tile, int32_t (&v)[kMaxTaps]) {
+    const bool has_rows = pw * 32u < tile_rows;  // else this warp only keeps the barriers going
+    int32_t* wring = sIdx + pw * (4 * kIdxSlot);
+
+    // Indices of one chunk: lane l copies the chunk's taps of row 32w + l (coalesced) into a
+    // slot of the warp's ring; taps past the kernel and rows past the end get -1.
+    auto issue_idx = [&](uint32_t tile, int j, uint32_t ring_slot) {
+      PROF(if (a.wait_test < 0 && ((-a.wait_test) & 4)) return;)
       const uint32_t row = tile * tile_rows + pw * 32u + lane;
-      const bool valid = tile < ntiles && row < n_out && pw * 32u < tile_rows;
-      const int32_t* src = a.map + row;
+      const bool valid = has_rows && tile < ntiles && row < n_out;
+      const int k0 = RB <= kChunk ? j * OPC : j / CPT;
+      const int32_t* src = a.map + (size_t)k0 * a.cap + row;
+      const uint32_t dst = smem_u32(wring + ring_slot * kIdxSlot + lane);
 #pragma unroll
-      for (int k = 0; k < kMaxTaps; ++k)
-        v[k] = (valid && k < a.kvol) ? __ldg(src + (size_t)k * a.cap) : -1;
+      for (int t = 0; t < OPC; ++t) {
+        if (valid && k0 + t < a.kvol) cp_async4(dst + t * (kIdxTapStride * 4), src + (size_t)t * a.cap);
+        else st_shared_s32(dst + t * (kIdxTapStride * 4), -1);
+      }
     };
-    // mbarrier traffic is kept per warp: one lane polls and broadcasts, one lane
-    // arrives after __syncwarp.
+    auto advance = [&](uint32_t& tile, int& j) {
+      if (++j == nchunk) {
+        j = 0;
+        tile += gridDim.x;
+      }
+    };
+    // mbarrier traffic is kept per warp: one lane polls and broadcasts.
     auto warp_wait = [&](uint32_t bar, uint32_t parity, uint32_t where) -> bool {
       uint32_t ok = 1u;
       if (lane == 0) ok = mbar_wait(bar, parity, abort_flag, a.status, where) ? 1u : 0u;
       return __shfl_sync(0xffffffffu, ok, 0) != 0u;
     };
-    uint32_t it = 0;
-    bool alive = true;
-    const bool has_rows = pw * 32u < tile_rows;  // else this warp only keeps the barriers going
-    int32_t nxt[kMaxTaps];
-    fetch_indices(blockIdx.x, nxt);
+    // L2 prefetch of what tile `pt` will read: its map lines (lanes 0-3 of every warp take
+    // the taps w, w+8, ...), its share of the input rows and its residual rows.  Bulk
+    // prefetches: one instruction per contiguous piece, nothing returns to the SM.
+    const uint32_t n_in = a.n_in_ptr ? min(*a.n_in_ptr, a.cap_in) : 0u;
+    const bool map_pf = (a.cap & 3u) == 0u && ((uintptr_t)a.map & 15u) == 0u;
+    auto prefetch_tile = [&](uint32_t pt) {
+      if (pt >= ntiles || lane > 4u) return;
+      const uint32_t prow0 = pt * tile_rows;
+      const uint32_t prows = min(tile_rows, n_out - prow0);
+      if (lane < 4u) {
+        const uint32_t k = pw + 8u * lane;
+        if (map_pf && k < (uint32_t)a.kvol)
+          bulk_prefetch_l2(a.map + (size_t)k * a.cap + prow0, ((prows + 3u) & ~3u) * 4u);
+      } else if (pw == 0u) {
+        if (n_in) {
+          const uint32_t in0 = (uint32_t)((unsigned long long)prow0 * n_in / n_out);
+          uint32_t cnt = (uint32_t)((unsigned long long)prows * n_in / n_out) + 1u;
+          if (in0 < n_in) {
+            cnt = min(cnt, n_in - in0);
+            bulk_prefetch_l2(a.in + (size_t)in0 * RB, cnt * (uint32_t)RB);
+          }
+        }
+      } else if (pw == 1u) {
+        if (a.ep.has_res) {
+          const uint32_t rb = (uint32_t)COUT * (a.ep.res_kind == SPCONVB_I8 ? 1u : 2u);
+          bulk_prefetch_l2(a.res + (size_t)prow0 * rb, prows * rb);
+        }
+      }
+    };
+    for (int p = 0; p < a.prefetch; ++p) prefetch_tile(blockIdx.x + (uint32_t)p * gridDim.x);
+
     if (r == 0 && w_resident && blockIdx.x < ntiles) {
       mbar_expect_tx(bar_w, (uint32_t)nchunk * w_chunk_smem);
       for (int j = 0; j < nchunk; ++j)
         for (uint32_t c = 0; c < w_rep; ++c)
-          bulk_g2s(smem_u32(sW + j * w_chunk_smem + c * kWChunk), a.wpk + (size_t)j * kWChunk,
-                   kWChunk, bar_w);
+          bulk_g2s(smem_u32(sW + j * w_chunk_smem + c * (COUT * kChunk)),
+                   a.wpk + (size_t)j * (COUT * kChunk), COUT * kChunk, bar_w);
     }
-    for (uint32_t tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x) {
-      __syncwarp();  // the warp's reads of the previous tile's indices are done
-#pragma unroll
-      for (int k = 0; k < kMaxTaps; ++k) widx[k * 32 + (lane & 3u) * 8u + (lane >> 2)] = nxt[k];
+
+    uint32_t g_tile = blockIdx.x, l_tile = blockIdx.x;  // gather and index-copy cursors
+    int g_j = 0, l_j = 0;
+    // The index ring (4 slots) runs three chunks ahead.  Every round commits one cp.async
+    // group: its row copies and, issued after them, the index copies of the chunk three
+    // rounds on.  The "stage full" arrival of a round therefore never waits for index copies
+    // issued in the same round, and the wait at the top of a round (all but the two newest
+    // groups) covers this round's indices while leaving two chunks of rows in flight.
+    for (uint32_t p = 0; p < 3; ++p) {
+      issue_idx(l_tile, l_j, p);
+      advance(l_tile, l_j);
+      cp_async_commit();
+    }
+    uint32_t it = 0, s = 0, ph = 0, rs = 0;
+    bool alive = true;
+    PROF(long long p_idx = 0, p_wait = 0, p_issue = 0, p_t0 = clock64(), t_a, t_b;)
+    PROF(const bool no_copies = a.wait_test < 0 && ((-a.wait_test) & 13);)
+    PROF(const bool warp_arrive = a.wait_test < 0 && ((-a.wait_test) & 8);)
+    while (g_tile < ntiles) {
+      PROF(t_a = clock64();)
+      cp_async_wait<2>();
       __syncwarp();
-      fetch_indices(tile + gridDim.x, nxt);
-      for (int j = 0; j < nchunk; ++j, ++it) {
-        const uint32_t s = it % kStages;
-        const uint32_t ph = (it / kStages) & 1u;
-        if (!warp_wait(bar_empty + 8 * s, ph ^ 1u, 1u)) {
-          alive = false;
-          break;
-        }
-        if (r == 0) {
-          if (w_resident) {
-            mbar_arrive(bar_full + 8 * s);
-          } else {
-            mbar_expect_tx(bar_full + 8 * s, w_chunk_smem);
-            for (uint32_t c = 0; c < w_rep; ++c)
-              bulk_g2s(smem_u32(sW + s * kWBytes + c * kWChunk), a.wpk + (size_t)j * kWChunk,
-                       kWChunk, bar_full + 8 * s);
-          }
-        }
-        const int k = (RB <= kChunk) ? j * OPC + (int)seg_tap : j / CPT;
-        const uint32_t byte = seg_byte + (RB > kChunk ? (uint32_t)(j % CPT) * kChunk : 0u);
-        // taps beyond the staged ones (K padding of the last chunk) gather nothing;
-        // staged taps beyond kvol hold -1
-        const bool staged = k < kMaxTaps;
-        if (has_rows) {
-          const int4* idx_k = (const int4*)(widx + (staged ? k : 0) * 32 + slot * 8u);
-          const uint32_t stage_addr = smem_u32(sR + s * kRowsBytes);
-          const int4 ia = idx_k[0], ib = idx_k[1];
-          int32_t src_row[8] = {ia.x, ia.y, ia.z, ia.w, ib.x, ib.y, ib.z, ib.w};
-#pragma unroll
-          for (int i = 0; i < 8; ++i) src_row[i] = staged ? src_row[i] : -1;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int32_t sr = src_row[i];
-            cp_async16(stage_addr + ((i & 1) ? dst_odd : dst_even) + (uint32_t)(i >> 1) * 1024u,
-                       a.in + (size_t)(sr < 0 ? 0 : sr) * RB + byte, sr < 0 ? 0u : 16u);
-          }
-        }
-        cp_async_commit();
-        if (it >= (uint32_t)kLag) {
-          cp_async_wait<kLag>();
-          fence_proxy_async();  // generic-proxy writes -> async-proxy reads of the MMA
-          __syncwarp();
-          if (lane == 0 && !(a.wait_test > 0 && it - kLag + 1u >= (uint32_t)a.wait_test))
-            mbar_arrive(bar_full + 8 * ((it - kLag) % kStages));
+      if (g_j == 0 && a.prefetch > 0) prefetch_tile(g_tile + (uint32_t)a.prefetch * gridDim.x);
+      PROF(t_b = clock64(); p_idx += t_b - t_a;)
+      if (!warp_wait(bar_empty + 8 * s, ph ^ 1u, 1u)) {
+        alive = false;
+        break;
+      }
+      PROF(t_a = clock64(); p_wait += t_a - t_b;)
+      if (r == 0) {
+        if (w_resident) {
+          mbar_arrive(bar_full + 8 * s);
+        } else {
+          mbar_expect_tx(bar_full + 8 * s, w_chunk_smem);
+          for (uint32_t c = 0; c < w_rep; ++c)
+            bulk_g2s(smem_u32(sW + s * w_chunk_smem + c * (COUT * kChunk)),
+                     a.wpk + (size_t)g_j * (COUT * kChunk), COUT * kChunk, bar_full + 8 * s);
         }
       }
+      if (has_rows PROF(&& !no_copies)) {
+        const uint32_t byte = seg_byte + (RB > kChunk ? (uint32_t)(g_j % CPT) * kChunk : 0u);
+        const int4* idx_k =
+            (const int4*)(wring + rs * kIdxSlot + seg_tap * kIdxTapStride + slot * 8u);
+        const int4 ia = idx_k[0], ib = idx_k[1];
+        const int32_t src_row[8] = {ia.x, ia.y, ia.z, ia.w, ib.x, ib.y, ib.z, ib.w};
+        const uint32_t stage_addr = smem_u32(sR + s * kRowsBytes) + dst_base;
+#pragma unroll
+        for (uint32_t i = 0; i < 8; ++i) {
+          const int32_t sr = src_row[i];
+          cp_async16(stage_addr + i * 128u + ((seg ^ i) << 4),
+                     a.in + (size_t)(sr < 0 ? 0 : sr) * RB + byte, sr < 0 ? 0u : 16u);
+        }
+      }
+      PROF(if (warp_arrive) { if (lane == 0) mbar_arrive(bar_full + 8 * s); } else)
+      if (!(a.wait_test > 0 && it + 1u >= (uint32_t)a.wait_test))
+        cp_async_arrive_noinc(bar_full + 8 * s);
+      issue_idx(l_tile, l_j, (rs + 3u) & 3u);
+      advance(l_tile, l_j);
+      cp_async_commit();
+      advance(g_tile, g_j);
+      ++it;
+      rs = (rs + 1u) & 3u;
+      if (++s == nst) {
+        s = 0;
+        ph ^= 1u;
+      }
+      PROF(p_issue += clock64() - t_a;)
     }
-    cp_async_wait<0>();
-    fence_proxy_async();
-    __syncwarp();
-    if (alive && lane == 0) {
-      const uint32_t first = it > (uint32_t)kLag ? it - kLag : 0u;
-      for (uint32_t i = first; i < it; ++i)
-        if (!(a.wait_test > 0 && i + 1u >= (uint32_t)a.wait_test))
-          mbar_arrive(bar_full + 8 * (i % kStages));
-    }
+    (void)alive;
+    PROF(if (pw == 7 && lane == 0 && blockIdx.x < 148) {
+      unsigned long long* o = g_conv_profile[blockIdx.x];
+      o[0] = clock64() - p_t0; o[1] = p_idx; o[2] = p_wait; o[3] = p_issue; o[4] = it;
+    })
+    cp_async_wait_all();  // nothing of this thread may still be writing when the CTA exits
   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------ MMA issue
     if (lane == 0) {
@@ -326,42 +381,83 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
       // second-to-last and the last MMA of a chunk, or is short: the next stage's
       // barrier is probed while the pipe is busy, so that the first MMA of the next
       // chunk can follow the last one of this chunk without a bubble.
-      const uint32_t idesc = make_idesc<INT8>() | ((tile_rows >> 3) << 17);
+      const uint32_t idesc =
+          make_idesc<INT8>() | ((tile_rows >> 3) << 17) | ((m_rows >> 4) << 24);
       const uint64_t wdesc0 = make_smem_desc(smem_u32(sW));  // M operand: weights
       const uint64_t rdesc0 = make_smem_desc(smem_u32(sR));  // N operand: gathered rows
-      uint32_t s = 0, ph = 0, tl = 0;
-      bool ready = false;  // full[s] already seen complete by a probe
+      uint32_t ph = 0, tl = 0;
       bool alive = true;
       if (w_resident && blockIdx.x < ntiles)
         alive = mbar_wait(bar_w, 0u, abort_flag, a.status, 6u);
+      // The loop is entered with the current chunk's stage known to be full.
+      if (blockIdx.x < ntiles && alive)
+        alive = mbar_wait(bar_full, 0u, abort_flag, a.status, 3u);
+      // The thread that issues the MMAs runs one lane of one warp: every instruction
+      // between two MMAs that the tensor pipe cannot hide (it queues about one MMA ahead)
+      // is a bubble.  So the loop carries its descriptors and barrier addresses along
+      // instead of recomputing them, asks about the next stage once, early (right after
+      // the first MMA, so the answer is there when the last one has been issued), and
+      // issues the K steps of a full chunk without a loop.
+      const uint32_t w_step = w_chunk_smem >> 4, r_step = (uint32_t)(kRowsBytes >> 4);
+      uint64_t rd = rdesc0;                       // rows of the current stage
+      uint64_t wd_s = wdesc0;                     // weights of the current stage (streamed)
+      uint32_t full_s = bar_full, empty_s = bar_empty;
+      const uint32_t full_end = bar_full + 8 * nst;
+      PROF(long long m_full = 0, m_issue = 0, m_tempty = 0, m_t0 = clock64(), t_a, t_b;)
+      PROF(const bool no_mma = a.wait_test < 0 && ((-a.wait_test) & 2);)
       for (uint32_t tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x, ++tl) {
         const uint32_t buf = tl & 1u;
+        PROF(t_a = clock64();)
         if (!mbar_wait(bar_tempty + 8 * buf, ((tl >> 1) & 1u) ^ 1u, abort_flag, a.status, 2u))
           break;
+        PROF(m_tempty += clock64() - t_a;)
+        tc_fence_after();  // the epilogue's reads of this accumulator come before these MMAs
         const uint32_t d_tmem = tmem_base + buf * kTileRows;
+        const bool last_tile = tile + gridDim.x >= ntiles;
+        uint64_t wd_r = wdesc0;                   // weights of the current chunk (resident)
         for (int j = 0; j < nchunk; ++j) {
-          if (!ready && !mbar_wait(bar_full + 8 * s, ph, abort_flag, a.status, 3u)) {
+          // No fence here: the rows arrive by cp.async completions on the stage's mbarrier,
+          // which is what the MMA's shared-memory reads are ordered behind.
+          const uint64_t wd = w_resident ? wd_r : wd_s;
+          // the next stage (of this tile's next chunk or of the next tile's first)
+          const bool wrap = full_s + 8 == full_end;
+          const uint32_t full_n = wrap ? bar_full : full_s + 8;
+          const uint32_t ph_n = wrap ? ph ^ 1u : ph;
+          const bool more = j + 1 < nchunk || !last_tile;
+          bool ready;
+          PROF(t_a = clock64();)
+          PROF(if (no_mma) ready = !more || mbar_test_wait(full_n, ph_n); else)
+          if (j + 1 < nchunk) {
+            umma<INT8>(d_tmem, wd, rd, idesc, (uint32_t)(j != 0));
+            ready = mbar_test_wait(full_n, ph_n);
+            umma<INT8>(d_tmem, wd + 2u, rd + 2u, idesc, 1u);
+            umma<INT8>(d_tmem, wd + 4u, rd + 4u, idesc, 1u);
+            umma<INT8>(d_tmem, wd + 6u, rd + 6u, idesc, 1u);
+          } else {
+            ready = !more || mbar_test_wait(full_n, ph_n);
+            for (int ks = 0; ks < last_ksteps; ++ks)
+              umma<INT8>(d_tmem, wd + 2u * ks, rd + 2u * ks, idesc, (uint32_t)((j | ks) != 0));
+          }
+          tc_commit(empty_s);
+          PROF(t_b = clock64(); m_issue += t_b - t_a;)
+          if (!ready && more && !mbar_wait(full_n, ph_n, abort_flag, a.status, 3u)) {
             alive = false;
             break;
           }
-          tc_fence_after();
-          const uint64_t wd = wdesc0 + (uint64_t)(w_resident ? (uint32_t)j * (w_chunk_smem >> 4)
-                                                             : s * (uint32_t)(kWBytes >> 4));
-          const uint64_t rd = rdesc0 + (uint64_t)(s * (uint32_t)(kRowsBytes >> 4));
-          const int nk = (j == nchunk - 1) ? last_ksteps : kChunk / 32;
-          for (int ks = 0; ks + 1 < nk; ++ks)
-            umma<INT8>(d_tmem, wd + 2u * ks, rd + 2u * ks, idesc, (uint32_t)((j | ks) != 0));
-          const uint32_t s1 = s + 1 == (uint32_t)kStages ? 0u : s + 1;
-          const uint32_t ph1 = s1 == 0u ? ph ^ 1u : ph;
-          ready = mbar_try_wait(bar_full + 8 * s1, ph1);
-          umma<INT8>(d_tmem, wd + 2u * (nk - 1), rd + 2u * (nk - 1), idesc,
-                     (uint32_t)((j | (nk - 1)) != 0));
-          tc_commit(bar_empty + 8 * s);
-          s = s1;
-          ph = ph1;
+          PROF(m_full += clock64() - t_b;)
+          full_s = full_n;
+          ph = ph_n;
+          empty_s = wrap ? bar_empty : empty_s + 8;
+          rd = wrap ? rdesc0 : rd + r_step;
+          wd_s = wrap ? wdesc0 : wd_s + w_step;
+          wd_r += w_step;
         }
         if (alive) tc_commit(bar_tfull + 8 * buf);
       }
+      PROF(if (blockIdx.x < 148) {
+        unsigned long long* o = g_conv_profile[blockIdx.x];
+        o[5] = clock64() - m_t0; o[6] = m_full; o[7] = m_issue; o[8] = m_tempty;
+      })
     }
     __syncwarp();
   } else {
@@ -371,23 +467,29 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
     // as one saturating round-to-nearest-even convert, and the layer-wide switches
     // hoisted out of the element loops.
     const Epilogue ep = a.ep;
-    // The weights are copied w_rep times along the accumulator lanes: lanes below
-    // w_rep * COUT hold a valid channel.  Copy r owns the tile's rows [r, r + 1) * 256 /
-    // w_rep, and the two warps of a lane quadrant split those rows again, so a warp works
-    // on 128 / w_rep rows of the tile: 8 / w_rep groups of 16.
+    // Accumulator row m holds channel m % COUT of weight copy m / COUT.  With 128 rows
+    // TMEM lane = m; with 64 rows the accumulator sits in lanes 0-15 of every 32-lane
+    // quadrant (m = 16 * quadrant + lane) and lanes 16-31 carry nothing.  Copy c owns the
+    // tile's rows [c, c + 1) * 256 / w_rep, and the two warps of a lane quadrant split
+    // those rows again, so a warp works on 128 / w_rep rows of the tile.
     const uint32_t q = (uint32_t)warp & 3u;        // TMEM lane quadrant of this warp
     const uint32_t half = (uint32_t)warp >> 2;
-    const uint32_t acc_lane = 32u * q + lane;
-    const uint32_t ch = acc_lane % COUT;           // this lane's channel
+    const bool wide = m_rows == 128u;
+    const bool lane_valid = wide || lane < 16u;
+    const uint32_t acc_row = wide ? 32u * q + lane : 16u * q + (lane & 15u);
+    const uint32_t acc_row0 = wide ? 32u * q : 16u * q;   // of lane 0 of the warp
+    const uint32_t ch = acc_row % COUT;            // this lane's channel
     const uint32_t chq = ch & ~3u;                 // first of the 4 channels this lane stores
     const uint32_t j4 = lane & 3u;                 // row within a group of 4 this lane stores
     const uint32_t cols_rep = (uint32_t)kTileRows / w_rep, cols_warp = cols_rep / 2u;
-    const bool lane_active = acc_lane / COUT < w_rep;
-    const bool warp_active = (32u * q) / COUT < w_rep;
+    const bool lane_active = lane_valid && acc_row / COUT < w_rep;
+    const bool warp_active = acc_row0 / COUT < w_rep;
     // first row (of the tile) of this lane, and of lane 0 of the warp: they differ only for
-    // COUT = 16, where the two halves of a warp belong to different copies
-    const uint32_t col_lane = (acc_lane / COUT) * cols_rep + half * cols_warp;
-    const uint32_t col_warp = ((32u * q) / COUT) * cols_rep + half * cols_warp;
+    // COUT = 16 with 128 accumulator rows, where the two halves of a warp belong to
+    // different copies
+    const bool split_warp = COUT == 16 && wide && w_rep > 1u;
+    const uint32_t col_lane = (acc_row / COUT) * cols_rep + half * cols_warp;
+    const uint32_t col_warp = (acc_row0 / COUT) * cols_rep + half * cols_warp;
     const float sc = (INT8 && a.scale) ? __ldg(a.scale + ch) : 1.f;
     const float bi = a.bias ? __ldg(a.bias + ch) : 0.f;
     const float lo = ep.act == SPCONVB_ACT_RELU ? 0.f : -INFINITY;
@@ -410,9 +512,11 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
       }
     };
     uint32_t tl = 0;
+    PROF(long long e_wait = 0, e_body = 0, e_t0 = clock64(), t_a, t_b;)
     for (uint32_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++tl) {
       const uint32_t buf = tl & 1u;
       const uint32_t trow0 = tile * tile_rows + col_lane;
+      PROF(t_a = clock64();)
       // the first residual rows are fetched before the accumulator is waited for;
       // after that the loads run one group of 16 rows ahead of the arithmetic.  A group
       // lies inside the tile or not as a whole (the tile height is a multiple of 32);
@@ -420,10 +524,16 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
       uint2 rq[4];
       if (ep.has_res) load_res(trow0, lane_active && col_lane < tile_rows, rq);
       uint32_t ok = 1u;
-      if (lane == 0)
+      if (lane == 0) {
+        PROF(if (a.wait_test < 0 && ((-a.wait_test) & 16)) {
+          for (int i = 0; i < 4000 && !mbar_test_wait(bar_tfull + 8 * buf, (tl >> 1) & 1u); ++i)
+            __nanosleep(500);
+        })
         ok = mbar_wait(bar_tfull + 8 * buf, (tl >> 1) & 1u, abort_flag, a.status, 4u) ? 1u : 0u;
+      }
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
+      PROF(t_b = clock64(); e_wait += t_b - t_a;)
       tc_fence_after();
       // groups of this warp that lie inside the tile (by its lower-numbered rows)
       const uint32_t ng = (!warp_active || col_warp >= tile_rows)
@@ -441,7 +551,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
         const bool in_tile = lane_active && col_lane + 16u * g < tile_rows;
         uint32_t v[16];
         tmem_ld16(taddr + 16u * g, v);
-        if (COUT == 16 && w_rep > 1u) {
+        if (split_warp) {
           // the upper half of the warp belongs to the next copy: its rows are one copy's
           // worth of columns further on
           uint32_t vm[16];
@@ -536,7 +646,12 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
           }
         }
       }
+      PROF(e_body += clock64() - t_b;)
     }
+    PROF(if (threadIdx.x == 0 && blockIdx.x < 148) {
+      unsigned long long* o = g_conv_profile[blockIdx.x];
+      o[9] = clock64() - e_t0; o[10] = e_wait; o[11] = e_body; o[12] = tl;
+    })
   }
 
   // ---------------------------------------------------------------- teardown
@@ -558,15 +673,15 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
 }
 
 template <bool INT8, int RB, int COUT>
-int launch_one(const UmmaArgs& args, uint32_t launch_rows, cudaStream_t st) {
+int launch_one(const UmmaArgs& args, uint32_t launch_rows, size_t smem, cudaStream_t st) {
   static bool attr_done[64] = {};
   int dev = 0;
   SPCONVB_CUDA_TRY(cudaGetDevice(&dev));
-  constexpr size_t smem = umma_smem_bytes();
+  if (smem > kMaxSmem) return SPCONVB_E_UNSUPPORTED;
   if (dev < 0 || dev >= 64 || !attr_done[dev]) {
     SPCONVB_CUDA_TRY(cudaFuncSetAttribute(conv_umma_kernel<INT8, RB, COUT>,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          (int)smem));
+                                          (int)kMaxSmem));
     if (dev >= 0 && dev < 64) attr_done[dev] = true;
   }
   uint32_t tiles = (launch_rows + 31) / 32;  // the kernel picks the tile height per launch
@@ -577,24 +692,26 @@ int launch_one(const UmmaArgs& args, uint32_t launch_rows, cudaStream_t st) {
 }
 
 template <bool INT8, int RB>
-int launch_cout(int cout, const UmmaArgs& args, uint32_t launch_rows, cudaStream_t st) {
+int launch_cout(int cout, const UmmaArgs& args, uint32_t launch_rows, size_t smem,
+                cudaStream_t st) {
   switch (cout) {
-    case 16: return launch_one<INT8, RB, 16>(args, launch_rows, st);
-    case 32: return launch_one<INT8, RB, 32>(args, launch_rows, st);
-    case 64: return launch_one<INT8, RB, 64>(args, launch_rows, st);
-    case 128: return launch_one<INT8, RB, 128>(args, launch_rows, st);
+    case 16: return launch_one<INT8, RB, 16>(args, launch_rows, smem, st);
+    case 32: return launch_one<INT8, RB, 32>(args, launch_rows, smem, st);
+    case 64: return launch_one<INT8, RB, 64>(args, launch_rows, smem, st);
+    case 128: return launch_one<INT8, RB, 128>(args, launch_rows, smem, st);
   }
   return SPCONVB_E_UNSUPPORTED;
 }
 
 template <bool INT8>
-int launch_rb(int rb, int cout, const UmmaArgs& args, uint32_t launch_rows, cudaStream_t st) {
+int launch_rb(int rb, int cout, const UmmaArgs& args, uint32_t launch_rows, size_t smem,
+              cudaStream_t st) {
   switch (rb) {
-    case 16: return launch_cout<INT8, 16>(cout, args, launch_rows, st);
-    case 32: return launch_cout<INT8, 32>(cout, args, launch_rows, st);
-    case 64: return launch_cout<INT8, 64>(cout, args, launch_rows, st);
-    case 128: return launch_cout<INT8, 128>(cout, args, launch_rows, st);
-    case 256: return launch_cout<INT8, 256>(cout, args, launch_rows, st);
+    case 16: return launch_cout<INT8, 16>(cout, args, launch_rows, smem, st);
+    case 32: return launch_cout<INT8, 32>(cout, args, launch_rows, smem, st);
+    case 64: return launch_cout<INT8, 64>(cout, args, launch_rows, smem, st);
+    case 128: return launch_cout<INT8, 128>(cout, args, launch_rows, smem, st);
+    case 256: return launch_cout<INT8, 256>(cout, args, launch_rows, smem, st);
   }
   return SPCONVB_E_UNSUPPORTED;
 }
@@ -602,9 +719,16 @@ int launch_rb(int rb, int cout, const UmmaArgs& args, uint32_t launch_rows, cuda
 }  // namespace
 
 int conv_umma_kernel_launch(const UmmaArgs& a, bool int8, int rb, int cout, uint32_t launch_rows,
-                       cudaStream_t st) {
-  return int8 ? launch_rb<true>(rb, cout, a, launch_rows, st)
-              : launch_rb<false>(rb, cout, a, launch_rows, st);
+                            size_t smem, cudaStream_t st) {
+  return int8 ? launch_rb<true>(rb, cout, a, launch_rows, smem, st)
+              : launch_rb<false>(rb, cout, a, launch_rows, smem, st);
 }
 
 }  // namespace spconvb
+
+#ifdef SPCONVB_CONV_PROFILE
+extern "C" __attribute__((visibility("default"))) int spconvb_debug_conv_profile(
+    unsigned long long* host) {
+  return (int)cudaMemcpyFromSymbol(host, spconvb::g_conv_profile, sizeof(spconvb::g_conv_profile));
+}
+#endif

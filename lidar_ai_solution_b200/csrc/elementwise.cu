@@ -20,9 +20,9 @@ __device__ __forceinline__ void store_q(void* p, int kind, float inv_scale, size
 template <int AK, int BK, int OK>
 __global__ void add_vec_kernel(const void* __restrict__ a, float a_scale,
                                const void* __restrict__ b, float b_scale, int channels,
-                               const uint32_t* n_ptr, int relu, float inv_out_scale,
-                               void* __restrict__ out) {
-  const size_t groups = (size_t)(*n_ptr) * channels / 16;
+                               const uint32_t* n_ptr, uint32_t cap, int relu,
+                               float inv_out_scale, void* __restrict__ out) {
+  const size_t groups = (size_t)min(*n_ptr, cap) * channels / 16;
   for (size_t gidx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; gidx < groups;
        gidx += (size_t)gridDim.x * blockDim.x) {
     float x[16], y[16];
@@ -81,8 +81,9 @@ __global__ void add_vec_kernel(const void* __restrict__ a, float a_scale,
 
 __global__ void add_scalar_kernel(const void* a, int a_kind, float a_scale, const void* b,
                                   int b_kind, float b_scale, int channels, const uint32_t* n_ptr,
-                                  int relu, int out_kind, float inv_out_scale, void* out) {
-  const size_t total = (size_t)(*n_ptr) * channels;
+                                  uint32_t cap, int relu, int out_kind, float inv_out_scale,
+                                  void* out) {
+  const size_t total = (size_t)min(*n_ptr, cap) * channels;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (size_t)gridDim.x * blockDim.x) {
     float y = __fadd_rn(load_deq(a, a_kind, a_scale, i), load_deq(b, b_kind, b_scale, i));
@@ -92,8 +93,8 @@ __global__ void add_scalar_kernel(const void* a, int a_kind, float a_scale, cons
 }
 
 __global__ void relu_kernel(const void* x, int kind, int channels, const uint32_t* n_ptr,
-                            void* out) {
-  const size_t total = (size_t)(*n_ptr) * channels;
+                            uint32_t cap, void* out) {
+  const size_t total = (size_t)min(*n_ptr, cap) * channels;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (size_t)gridDim.x * blockDim.x) {
     if (kind == SPCONVB_I8) {
@@ -125,8 +126,8 @@ __global__ void absmax_kernel(const void* x, int kind, int channels, const uint3
 }
 
 __global__ void convert_kernel(const void* x, int in_kind, int cin, int out_kind, int cout,
-                               float s, const uint32_t* n_ptr, void* out) {
-  const size_t total = (size_t)(*n_ptr) * cout;
+                               float s, const uint32_t* n_ptr, uint32_t cap, void* out) {
+  const size_t total = (size_t)min(*n_ptr, cap) * cout;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (size_t)gridDim.x * blockDim.x) {
     const size_t row = i / cout;
@@ -148,16 +149,32 @@ __global__ void convert_kernel(const void* x, int in_kind, int cin, int out_kind
   }
 }
 
+// fp16 rows padded to 8 channels (the first layer of a lidar backbone: 4 or 5 point features in
+// 16-byte rows): one thread per row, one 16-byte store.
+__global__ void pad8_f16_kernel(const __half* __restrict__ x, int cin, const uint32_t* n_ptr,
+                                uint32_t cap, uint4* __restrict__ out) {
+  const uint32_t n = min(*n_ptr, cap);
+  for (uint32_t row = blockIdx.x * blockDim.x + threadIdx.x; row < n;
+       row += gridDim.x * blockDim.x) {
+    const __half* src = x + (size_t)row * cin;
+    uint16_t h[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) h[c] = c < cin ? __half_as_ushort(__ldg(src + c)) : (uint16_t)0;
+    out[row] = make_uint4(h[0] | (uint32_t)h[1] << 16, h[2] | (uint32_t)h[3] << 16,
+                          h[4] | (uint32_t)h[5] << 16, h[6] | (uint32_t)h[7] << 16);
+  }
+}
+
 // 32 rows per block: rows are read coalesced into shared memory, then written
 // channel by channel so that neighbouring rows (neighbouring cells when the
 // rows are in canonical order) share write sectors.
 __global__ void scatter_dense_kernel(const void* __restrict__ feat, int in_kind, float in_scale,
                                      const int4* __restrict__ coords, const uint32_t* n_ptr,
-                                     int channels, Grid3 g, int p0, int p1, int p2,
+                                     uint32_t cap, int channels, Grid3 g, int p0, int p1, int p2,
                                      __half* __restrict__ out) {
   extern __shared__ __half tile[];  // [channels][33]
   __shared__ long long s_cell[32];
-  const uint32_t n = *n_ptr;
+  const uint32_t n = min(*n_ptr, cap);
   const int gp[3] = {g.g[p0], g.g[p1], g.g[p2]};
   const size_t vol = (size_t)gp[0] * gp[1] * gp[2];
   for (uint32_t row0 = blockIdx.x * 32; row0 < n; row0 += gridDim.x * 32) {
@@ -205,10 +222,11 @@ __global__ void scatter_dense_kernel(const void* __restrict__ feat, int in_kind,
 template <typename OutT>
 __global__ void scatter_dense_layout_kernel(const void* __restrict__ feat, int in_kind,
                                             float in_scale, const int4* __restrict__ coords,
-                                            const uint32_t* n_ptr, int channels, Grid3 g, int p0,
-                                            int p1, int p2, int layout, float inv_out,
-                                            int copy_bytes, OutT* __restrict__ out) {
-  const size_t total = (size_t)(*n_ptr) * channels;
+                                            const uint32_t* n_ptr, uint32_t cap, int channels,
+                                            Grid3 g, int p0, int p1, int p2, int layout,
+                                            float inv_out, int copy_bytes,
+                                            OutT* __restrict__ out) {
+  const size_t total = (size_t)min(*n_ptr, cap) * channels;
   const int g0 = g.g[p0], g1 = g.g[p1], g2 = g.g[p2];
   const long long plane = (long long)g1 * g2;
   const long long merged = (long long)channels * g0;
@@ -268,8 +286,8 @@ int spconvb_add(const void* a, int32_t a_kind, float a_scale, const void* b, int
     const int blocks = blocks_for(groups, 256);
 #define SPCONVB_ADD_CASE(AK, BK, OK)                                                        \
   if (a_kind == AK && b_kind == BK && out_kind == OK) {                                     \
-    add_vec_kernel<AK, BK, OK><<<blocks, 256, 0, st>>>(a, a_scale, b, b_scale, channels,    \
-                                                       n_ptr, relu, inv_out_scale, out);    \
+    add_vec_kernel<AK, BK, OK><<<blocks, 256, 0, st>>>(                                     \
+        a, a_scale, b, b_scale, channels, n_ptr, launch_rows, relu, inv_out_scale, out);    \
     SPCONVB_LAUNCH_CHECK();                                                                 \
     return SPCONVB_OK;                                                                      \
   }
@@ -281,8 +299,8 @@ int spconvb_add(const void* a, int32_t a_kind, float a_scale, const void* b, int
   }
   const uint32_t work = clamp_u32((size_t)launch_rows * channels);
   add_scalar_kernel<<<blocks_for(work, 256), 256, 0, st>>>(a, a_kind, a_scale, b, b_kind, b_scale,
-                                                           channels, n_ptr, relu, out_kind,
-                                                           inv_out_scale, out);
+                                                           channels, n_ptr, launch_rows, relu,
+                                                           out_kind, inv_out_scale, out);
   SPCONVB_LAUNCH_CHECK();
   return SPCONVB_OK;
 }
@@ -292,7 +310,7 @@ int spconvb_relu(const void* x, int32_t kind, int32_t channels, const uint32_t* 
   if (!x || !out || !n_ptr || channels < 1 || launch_rows < 1) return SPCONVB_E_ARG;
   const uint32_t work = clamp_u32((size_t)launch_rows * channels);
   relu_kernel<<<blocks_for(work, 256), 256, 0, (cudaStream_t)stream>>>(x, kind, channels, n_ptr,
-                                                                       out);
+                                                                       launch_rows, out);
   SPCONVB_LAUNCH_CHECK();
   return SPCONVB_OK;
 }
@@ -311,9 +329,16 @@ int spconvb_convert(const void* x, int32_t in_kind, int32_t cin, int32_t out_kin
                     int32_t cout_pad, float scale_or_inv, const uint32_t* n_ptr,
                     uint32_t launch_rows, void* out, void* stream) {
   if (!x || !out || !n_ptr || cin < 1 || cout_pad < cin || launch_rows < 1) return SPCONVB_E_ARG;
+  if (in_kind == SPCONVB_F16 && out_kind == SPCONVB_F16 && cout_pad == 8 &&
+      !((uintptr_t)out & 15u)) {
+    pad8_f16_kernel<<<blocks_for(launch_rows, 128), 128, 0, (cudaStream_t)stream>>>(
+        (const __half*)x, cin, n_ptr, launch_rows, (uint4*)out);
+    SPCONVB_LAUNCH_CHECK();
+    return SPCONVB_OK;
+  }
   const uint32_t work = clamp_u32((size_t)launch_rows * cout_pad);
   convert_kernel<<<blocks_for(work, 256), 256, 0, (cudaStream_t)stream>>>(
-      x, in_kind, cin, out_kind, cout_pad, scale_or_inv, n_ptr, out);
+      x, in_kind, cin, out_kind, cout_pad, scale_or_inv, n_ptr, launch_rows, out);
   SPCONVB_LAUNCH_CHECK();
   return SPCONVB_OK;
 }
@@ -331,6 +356,20 @@ int spconvb_scatter_dense(const void* feat, int32_t in_kind, float in_scale,
     if ((1 << p[0] | 1 << p[1] | 1 << p[2]) != 7) return SPCONVB_E_ARG;
   }
   cudaStream_t st = (cudaStream_t)stream;
+  const size_t tile_bytes = sizeof(__half) * 33 * (size_t)channels;
+  if (tile_bytes > 48 * 1024) {
+    // wider rows than the default shared-memory window: raise the kernel's limit (once per
+    // device; channels <= 1024 needs 66 KB)
+    static bool raised[64] = {};
+    int dev = 0;
+    SPCONVB_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !raised[dev]) {
+      SPCONVB_CUDA_TRY(cudaFuncSetAttribute(scatter_dense_kernel,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            (int)(sizeof(__half) * 33 * 1024)));
+      if (dev >= 0 && dev < 64) raised[dev] = true;
+    }
+  }
   Grid3 g;
   g.g[0] = grid[0]; g.g[1] = grid[1]; g.g[2] = grid[2];
   g.batch = batch;
@@ -340,8 +379,8 @@ int spconvb_scatter_dense(const void* feat, int32_t in_kind, float in_scale,
   if (want_blocks > (size_t)kSmCount * 16) want_blocks = (size_t)kSmCount * 16;
   const int blocks = (int)want_blocks;
   scatter_dense_kernel<<<blocks, 256, sizeof(__half) * 33 * channels, st>>>(
-      feat, in_kind, in_scale, (const int4*)coords, n_ptr, channels, g, p[0], p[1], p[2],
-      (__half*)out);
+      feat, in_kind, in_scale, (const int4*)coords, n_ptr, launch_rows, channels, g, p[0], p[1],
+      p[2], (__half*)out);
   SPCONVB_LAUNCH_CHECK();
   return SPCONVB_OK;
 }
@@ -379,12 +418,12 @@ int spconvb_scatter_dense_layout(const void* feat, int32_t in_kind, float in_sca
   const int blocks = blocks_for(work, 256);
   if (out_kind == SPCONVB_I8)
     scatter_dense_layout_kernel<int8_t><<<blocks, 256, 0, st>>>(
-        feat, in_kind, in_scale, (const int4*)coords, n_ptr, channels, g, p[0], p[1], p[2], layout,
-        inv_out_scale, copy_bytes, (int8_t*)out);
+        feat, in_kind, in_scale, (const int4*)coords, n_ptr, launch_rows, channels, g, p[0], p[1],
+        p[2], layout, inv_out_scale, copy_bytes, (int8_t*)out);
   else
     scatter_dense_layout_kernel<__half><<<blocks, 256, 0, st>>>(
-        feat, in_kind, in_scale, (const int4*)coords, n_ptr, channels, g, p[0], p[1], p[2], layout,
-        inv_out_scale, 0, (__half*)out);
+        feat, in_kind, in_scale, (const int4*)coords, n_ptr, launch_rows, channels, g, p[0], p[1],
+        p[2], layout, inv_out_scale, 0, (__half*)out);
   SPCONVB_LAUNCH_CHECK();
   return SPCONVB_OK;
 }

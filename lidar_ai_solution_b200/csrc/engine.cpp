@@ -704,10 +704,16 @@ int Engine::prepare(const int32_t grid[3], int batch) {
   batch_ = batch;
 
   // capacities and grids, in creation order (inputs of a rule come before its outputs)
+  // output_bound is what one frame may hold (the reference runs one frame per call): a
+  // batch of frames gets that much room per frame
+  auto batch_cap = [&](uint32_t per_frame) {
+    const unsigned long long v = (unsigned long long)(per_frame ? per_frame : 200000u) * batch;
+    return (uint32_t)std::min(v, 0x7fffffffull);
+  };
   for (auto& cs : coordsets)
     if (cs.external) {
       for (int a = 0; a < 3; ++a) cs.grid[a] = grid[a];
-      cs.cap = cs.bound ? cs.bound : 200000u;
+      cs.cap = batch_cap(cs.bound);
     }
   for (auto& R : rules) {
     if (R.subm || R.inverse_of >= 0) continue;
@@ -722,7 +728,7 @@ int Engine::prepare(const int32_t grid[3], int batch) {
       }
       cells *= out.grid[a];
     }
-    unsigned long long cap = out.bound ? out.bound : 200000u;
+    unsigned long long cap = batch_cap(out.bound);
     unsigned long long reach = (unsigned long long)in.cap * R.kvol;
     out.cap = (uint32_t)std::min(std::min(cap, cells), reach);
     R.ws_bytes = spconvb_down_workspace_bytes(out.grid, batch);
@@ -782,6 +788,9 @@ int Engine::prepare(const int32_t grid[3], int batch) {
     RTensor& t = rt[r];
     if (t.external || t.alias_of >= 0) continue;
     if (t.dense) {
+      // the model writes the dense shape for one frame: the leading dimension is the batch
+      if (!t.shape.empty()) t.shape[0] = batch;
+      if (!t.phys_shape.empty()) t.phys_shape[0] = batch;
       size_t numel = 1;
       for (auto v : t.phys_shape) numel *= (size_t)v;
       t.bytes = numel * (t.kind == SPCONVB_I8 ? 1 : sizeof(uint16_t));
@@ -836,13 +845,14 @@ int Engine::forward(const void* features, const int32_t* indices, uint32_t cap_r
   cudaError_t ce = cudaMemsetAsync(zero_arena_, 0, zero_bytes_, st);
   if (ce != cudaSuccess) return (int)ce;
   const uint32_t in_cap = n_dev ? std::min(cap_rows, in.cap) : in.cap;
-  const uint32_t* in_n = n_dev;
-  if (!n_dev) {
-    uint32_t* slot = counts_ + 64 * (size_t)rt[input_rt_].cs;
-    if ((rc = launch_set_count(slot, n_host, st)) != SPCONVB_OK) return rc;
-    ++last_launches;
-    in_n = slot;
-  }
+  // Every step reads the input's row count from the engine's own word: the host's value, or
+  // the caller's device-side value clamped to the rows the caller's buffers (and the model's
+  // bound) hold, so that no kernel can be led past them.
+  uint32_t* in_n = counts_ + 64 * (size_t)rt[input_rt_].cs;
+  if (n_dev) rc = launch_clamp_count(in_n, n_dev, in_cap, status, st);
+  else rc = launch_set_count(in_n, n_host, st);
+  if (rc != SPCONVB_OK) return rc;
+  ++last_launches;
   rt[input_rt_].data = const_cast<void*>(features);
   last_in_n_ = in_n;
   last_in_cap_ = in_cap;
@@ -888,7 +898,7 @@ int Engine::forward(const void* features, const int32_t* indices, uint32_t cap_r
                               cs_launch(R.in_cs), ci.grid, batch, R.ksize, R.stride, R.pad, R.dil,
                               ci.table, ci.slots, R.ws, co.coords, co.n_ptr, co.cap, R.map,
                               co.table, co.slots, SPCONVB_FLAG_PREZEROED, status, st);
-        last_launches += 4;
+        last_launches += 5 + (co.table ? 1 : 0);  // mark, scan, emit, map fill, scatter (+ hash)
         break;
       }
       case Step::INV_MAP: {
@@ -911,6 +921,8 @@ int Engine::forward(const void* features, const int32_t* indices, uint32_t cap_r
         const LayerWeights& w = weights[s.weights];
         spconvb_conv_params p = s.cp;
         p.res = s.in1 >= 0 ? rt[s.in1].data : nullptr;
+        p.n_in_ptr = cs_n(R.in_cs);
+        p.cap_in = cs_cap(R.in_cs);
         rc = spconvb_conv_forward(&p, rt[s.in0].data, R.map, coordsets[R.out_cs].cap,
                                   cs_n(R.out_cs), cs_launch(R.out_cs), w.plain, w.packed, w.scale,
                                   w.bias, rt[s.out].data, status, st);
@@ -934,7 +946,7 @@ int Engine::forward(const void* features, const int32_t* indices, uint32_t cap_r
                                           cs_coords(s.cs), cs_n(s.cs), cs_launch(s.cs), s.cout,
                                           batch, cs.grid, s.has_perm ? s.perm : nullptr, s.layout,
                                           rt[s.out].kind, s.inv_out, rt[s.out].data, st);
-        last_launches += 1;
+        last_launches += 2;  // the zero fill and the scatter
         break;
       }
     }

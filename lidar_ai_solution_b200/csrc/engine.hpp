@@ -18,6 +18,8 @@ void log_msg(int level, const char* fmt, ...);
 enum { LOG_VERB = 0, LOG_WARN = 1, LOG_ERROR = 2 };
 
 int launch_set_count(uint32_t* dst, uint32_t value, cudaStream_t st);
+int launch_clamp_count(uint32_t* dst, const uint32_t* src, uint32_t cap, uint32_t* status,
+                       cudaStream_t st);
 
 enum OpKind { OP_INPUT, OP_CONV, OP_ADD, OP_RELU, OP_DENSE, OP_RESHAPE, OP_TRANSPOSE };
 

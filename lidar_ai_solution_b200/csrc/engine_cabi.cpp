@@ -420,6 +420,22 @@ int spconvb_engine_output_layout(const spconvb_engine* e, int i, int32_t* layout
   return SPCONVB_OK;
 }
 
+int spconvb_engine_output_rows(const spconvb_engine* e, int i, int32_t** coords,
+                               uint32_t** n_ptr, uint32_t* cap, int32_t grid[3],
+                               int32_t* on_input_rows) {
+  if (!e || i < 0 || i >= (int)e->e->outputs.size()) return SPCONVB_E_ARG;
+  const RTensor& t = e->e->rt[e->e->outputs[i]];
+  if (t.dense || t.cs < 0) return SPCONVB_E_ARG;
+  const CoordSet& cs = e->e->coordsets[t.cs];
+  if (coords) *coords = cs.external ? nullptr : cs.coords;
+  if (n_ptr) *n_ptr = cs.n_ptr;
+  if (cap) *cap = cs.cap;
+  if (grid)
+    for (int a = 0; a < 3; ++a) grid[a] = cs.grid[a];
+  if (on_input_rows) *on_input_rows = cs.external ? 1 : 0;
+  return SPCONVB_OK;
+}
+
 int spconvb_engine_tensor(const spconvb_engine* e, const char* name, spconvb_tensor_view* v) {
   if (!e || !name || !v) return SPCONVB_E_ARG;
   auto it = e->e->by_name.find(name);

@@ -172,6 +172,10 @@ class EngineImpl : public Engine {
 
  private:
   // Point the output tensors at the engine's buffers (they exist after the first forward).
+  // A sparse output also gets its indices and grid.  Its row count lives in device memory
+  // (nothing here waits for the stream): get_dds_num_of_points_pointer() of the output gives
+  // that word, rows beyond it are undefined, and the shapes report the capacity - except for
+  // an output on the input's own rows with a host-known count, which reports that count.
   void refresh_outputs() {
     for (size_t i = 0; i < outputs_.size(); ++i) {
       void* data = nullptr;
@@ -179,7 +183,26 @@ class EngineImpl : public Engine {
       int32_t ndim = 0, kind = 0, dense = 0;
       if (spconvb_engine_output(e_, (int)i, &data, shape, &ndim, &kind, &dense) != SPCONVB_OK) continue;
       std::vector<int64_t> s(shape, shape + ndim);
-      outputs_[i]->features_.reference(data, s, kind == SPCONVB_I8 ? DataType::Int8 : DataType::Float16);
+      SparseTensorImpl& out = *outputs_[i];
+      if (!dense) {
+        int32_t* coords = nullptr;
+        uint32_t* n_ptr = nullptr;
+        uint32_t cap = 0;
+        int32_t grid[3] = {0, 0, 0}, on_input = 0;
+        if (spconvb_engine_output_rows(e_, (int)i, &coords, &n_ptr, &cap, grid, &on_input) == SPCONVB_OK) {
+          const SparseTensorImpl& in = *inputs_[0];
+          int64_t rows = cap;
+          if (on_input && !in.indices_.empty()) {
+            coords = const_cast<int32_t*>(in.indices_.ptr<int32_t>());
+            if (!in.dds_) rows = in.features_.size(0);
+          }
+          if (!s.empty()) s[0] = rows;
+          if (coords) out.indices_.reference(coords, std::vector<int64_t>{rows, 4}, DataType::Int32);
+          out.grid_ = {grid[0], grid[1], grid[2]};
+          out.dds_ = n_ptr;
+        }
+      }
+      out.features_.reference(data, s, kind == SPCONVB_I8 ? DataType::Int8 : DataType::Float16);
     }
   }
 
@@ -304,9 +327,13 @@ class BuilderImpl : public EngineBuilder {
     if (value) spconvb_builder_output(b_, id_of(value));
   }
 
-  std::shared_ptr<Engine> build(Precision precision, bool, bool, bool, void* stream) override {
+  // sortmask and enable_blackwell select kernels of the reference's engine and mean nothing
+  // here; with_auxiliary_stream = false keeps the rulebook kernels on the caller's stream.
+  std::shared_ptr<Engine> build(Precision precision, bool, bool, bool with_auxiliary_stream,
+                                void* stream) override {
     int err = 0;
-    spconvb_engine* e = spconvb_builder_build(b_, prec(precision), 0, stream, &err);
+    spconvb_engine* e = spconvb_builder_build(
+        b_, prec(precision), with_auxiliary_stream ? 0u : SPCONVB_BUILD_SINGLE_STREAM, stream, &err);
     if (!e) {
       logger_output(__FILE__, __LINE__, LoggerLevel::Error, "build failed: %s", spconvb_error_string(err));
       return nullptr;
@@ -348,11 +375,12 @@ class BuilderImpl : public EngineBuilder {
 std::shared_ptr<EngineBuilder> create_engine_builder() { return std::make_shared<BuilderImpl>(); }
 
 std::shared_ptr<Engine> load_engine_from_onnx(const std::string& onnx_file, Precision inference_precision,
-                                              bool, bool, bool, unsigned int fixed_launch_points,
-                                              void* stream) {
+                                              bool, bool, bool with_auxiliary_stream,
+                                              unsigned int fixed_launch_points, void* stream) {
   int err = 0;
-  spconvb_engine* e = spconvb_engine_load_onnx(onnx_file.c_str(), prec(inference_precision), 0,
-                                               fixed_launch_points, stream, &err);
+  spconvb_engine* e = spconvb_engine_load_onnx(
+      onnx_file.c_str(), prec(inference_precision),
+      with_auxiliary_stream ? 0u : SPCONVB_BUILD_SINGLE_STREAM, fixed_launch_points, stream, &err);
   if (!e) {
     logger_output(__FILE__, __LINE__, LoggerLevel::Error, "load_engine_from_onnx(%s) failed: %s",
                   onnx_file.c_str(), spconvb_error_string(err));

@@ -43,32 +43,49 @@ struct Kernel3 {
   int32_t d[3];
 };
 
+// One thread per row: the row's coordinate is read once, its taps are walked in tap order
+// (so a warp's stores of one tap land in one or two lines of map[k][.]), and the lookups of
+// the 27 taps are independent loads the compiler overlaps when the kernel size is known at
+// compile time (K333: the 3x3x3, dilation-1 case of every backbone layer).
+template <bool K333, typename Lookup>
+__device__ __forceinline__ void subm_row_taps(const int4 c, uint32_t row, const Grid3& g,
+                                              const Kernel3& kr, uint32_t cap,
+                                              int32_t* __restrict__ map, Lookup lookup) {
+  const int K0 = K333 ? 3 : kr.k[0], K1 = K333 ? 3 : kr.k[1], K2 = K333 ? 3 : kr.k[2];
+  const int D0 = K333 ? 1 : kr.d[0], D1 = K333 ? 1 : kr.d[1], D2 = K333 ? 1 : kr.d[2];
+  const bool bok = (unsigned)c.x < (unsigned)g.batch;
+  int32_t* dst = map + row;
+#pragma unroll
+  for (int k0 = 0; k0 < K0; ++k0) {
+    const int p0 = c.y + (k0 - K0 / 2) * D0;
+    const bool ok0 = bok && (unsigned)p0 < (unsigned)g.g[0];
+#pragma unroll
+    for (int k1 = 0; k1 < K1; ++k1) {
+      const int p1 = c.z + (k1 - K1 / 2) * D1;
+      const bool ok1 = ok0 && (unsigned)p1 < (unsigned)g.g[1];
+#pragma unroll
+      for (int k2 = 0; k2 < K2; ++k2) {
+        const int p2 = c.w + (k2 - K2 / 2) * D2;
+        int32_t r = -1;
+        if (k0 == K0 / 2 && k1 == K1 / 2 && k2 == K2 / 2) r = (int32_t)row;
+        else if (ok1 && (unsigned)p2 < (unsigned)g.g[2]) r = lookup(voxel_key(c.x, p0, p1, p2, g));
+        *dst = r;
+        dst += cap;
+      }
+    }
+  }
+}
+
+template <bool K333>
 __global__ void subm_map_kernel(const int4* __restrict__ coords, const uint32_t* n_ptr,
-                                uint32_t cap, Grid3 g, Kernel3 kr, int kvol,
+                                uint32_t cap, Grid3 g, Kernel3 kr,
                                 const uint64_t* __restrict__ table, uint32_t mask,
                                 int32_t* __restrict__ map) {
   const uint32_t n = min(*n_ptr, cap);
-  const unsigned long long work = (unsigned long long)n * kvol;
-  for (unsigned long long idx = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
-       idx < work; idx += (unsigned long long)gridDim.x * blockDim.x) {
-    const int k = (int)(idx / n);
-    const uint32_t row = (uint32_t)(idx - (unsigned long long)k * n);
-    const int k2 = k % kr.k[2], k1 = (k / kr.k[2]) % kr.k[1], k0 = k / (kr.k[2] * kr.k[1]);
-    const int d0 = (k0 - kr.k[0] / 2) * kr.d[0];
-    const int d1 = (k1 - kr.k[1] / 2) * kr.d[1];
-    const int d2 = (k2 - kr.k[2] / 2) * kr.d[2];
-    int32_t r = -1;
-    if ((d0 | d1 | d2) == 0) {
-      r = (int32_t)row;
-    } else {
-      int4 c = __ldg(coords + row);
-      int p0 = c.y + d0, p1 = c.z + d1, p2 = c.w + d2;
-      if ((unsigned)p0 < (unsigned)g.g[0] && (unsigned)p1 < (unsigned)g.g[1] &&
-          (unsigned)p2 < (unsigned)g.g[2] && (unsigned)c.x < (unsigned)g.batch)
-        r = hash_lookup(table, mask, voxel_key(c.x, p0, p1, p2, g));
-    }
-    map[(size_t)k * cap + row] = r;
-  }
+  for (uint32_t row = blockIdx.x * blockDim.x + threadIdx.x; row < n;
+       row += gridDim.x * blockDim.x)
+    subm_row_taps<K333>(__ldg(coords + row), row, g, kr, cap, map,
+                        [&](uint32_t key) { return hash_lookup(table, mask, key); });
 }
 
 // ---------------------------------------------------------------- strided map
@@ -299,35 +316,34 @@ __global__ void hash_rows_kernel(const int4* __restrict__ coords, const uint32_t
 }
 
 // Submanifold map of a coordinate set that came out of down_map: neighbours are
-// found by rank in that set's bitmap, no hash table involved.  One thread per
-// (row, tap).
+// found by rank in that set's bitmap, no hash table involved.  One thread per row;
+// rows are in cell order, so a warp's lookups of one tap fall into the same or
+// adjacent bitmap words and its map stores coalesce.
+template <bool K333>
 __global__ void subm_ranked_kernel(const int4* __restrict__ coords, const uint32_t* n_ptr,
-                                   uint32_t cap, Grid3 g, Kernel3 kr, int kvol, DownWs ws,
+                                   uint32_t cap, Grid3 g, Kernel3 kr, DownWs ws,
                                    int32_t* __restrict__ map) {
   const uint32_t n = min(*n_ptr, cap);
-  const unsigned long long work = (unsigned long long)n * kvol;
-  for (unsigned long long idx = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
-       idx < work; idx += (unsigned long long)gridDim.x * blockDim.x) {
-    // consecutive threads take consecutive rows of one tap: the map stores coalesce, and
-    // rows are in cell order, so their lookups fall into the same or adjacent bitmap words
-    const int k = (int)(idx / n);
-    const uint32_t row = (uint32_t)(idx - (unsigned long long)k * n);
-    const int k2 = k % kr.k[2], k1 = (k / kr.k[2]) % kr.k[1], k0 = k / (kr.k[2] * kr.k[1]);
-    const int d0 = (k0 - kr.k[0] / 2) * kr.d[0];
-    const int d1 = (k1 - kr.k[1] / 2) * kr.d[1];
-    const int d2 = (k2 - kr.k[2] / 2) * kr.d[2];
-    int32_t r = -1;
-    if ((d0 | d1 | d2) == 0) {
-      r = (int32_t)row;
-    } else {
-      const int4 c = __ldg(coords + row);
-      const int p0 = c.y + d0, p1 = c.z + d1, p2 = c.w + d2;
-      if ((unsigned)p0 < (unsigned)g.g[0] && (unsigned)p1 < (unsigned)g.g[1] &&
-          (unsigned)p2 < (unsigned)g.g[2] && (unsigned)c.x < (unsigned)g.batch)
-        r = rank_lookup(ws.bitmap, ws.prefix, voxel_key(c.x, p0, p1, p2, g), cap);
-    }
-    map[(size_t)k * cap + row] = r;
-  }
+  for (uint32_t row = blockIdx.x * blockDim.x + threadIdx.x; row < n;
+       row += gridDim.x * blockDim.x)
+    subm_row_taps<K333>(__ldg(coords + row), row, g, kr, cap, map, [&](uint32_t key) {
+      return rank_lookup(ws.bitmap, ws.prefix, key, cap);
+    });
+}
+
+// Blocks for one thread per row: small blocks, so that a few thousand rows still spread
+// over the SMs, capped at a few waves (the kernels stride).
+static int row_blocks(uint32_t rows, int threads) {
+  unsigned long long b = ((unsigned long long)rows + threads - 1) / threads;
+  const unsigned long long most = (unsigned long long)kSmCount * 16;
+  if (b > most) b = most;
+  if (b < 1) b = 1;
+  return (int)b;
+}
+
+static bool is_k333(const Kernel3& kr) {
+  return kr.k[0] == 3 && kr.k[1] == 3 && kr.k[2] == 3 && kr.d[0] == 1 && kr.d[1] == 1 &&
+         kr.d[2] == 1;
 }
 
 // Fixed-size grids: a multiple of the SM count, independent of the row count.
@@ -432,10 +448,14 @@ int spconvb_subm_map(const int32_t* coords, const uint32_t* n_ptr, uint32_t cap,
   const int kvol = ksize[0] * ksize[1] * ksize[2];
   if (kvol > 65535) return SPCONVB_E_ARG;
   if (launch_rows == 0 || launch_rows > cap) launch_rows = cap;
-  subm_map_kernel<<<flat_blocks((unsigned long long)launch_rows * kvol), kThreads, 0,
-                    (cudaStream_t)stream>>>((const int4*)coords, n_ptr, cap,
-                                            make_grid(grid, batch), kr, kvol, table, slots - 1,
-                                            map);
+  constexpr int kRowThreads = 128;
+  const int blocks = row_blocks(launch_rows, kRowThreads);
+  if (is_k333(kr))
+    subm_map_kernel<true><<<blocks, kRowThreads, 0, (cudaStream_t)stream>>>(
+        (const int4*)coords, n_ptr, cap, make_grid(grid, batch), kr, table, slots - 1, map);
+  else
+    subm_map_kernel<false><<<blocks, kRowThreads, 0, (cudaStream_t)stream>>>(
+        (const int4*)coords, n_ptr, cap, make_grid(grid, batch), kr, table, slots - 1, map);
   SPCONVB_LAUNCH_CHECK();
   return SPCONVB_OK;
 }
@@ -463,9 +483,14 @@ int spconvb_subm_map_ranked(const int32_t* coords, const uint32_t* n_ptr, uint32
   ws.prefix = ws.bitmap + ws.words;
   ws.block_sums = ws.prefix + ws.words;
   if (launch_rows == 0 || launch_rows > cap) launch_rows = cap;
-  subm_ranked_kernel<<<flat_blocks((unsigned long long)launch_rows * kvol), kThreads, 0,
-                       (cudaStream_t)stream>>>((const int4*)coords, n_ptr, cap,
-                                               make_grid(grid, batch), kr, kvol, ws, map);
+  constexpr int kRowThreads = 128;
+  const int blocks = row_blocks(launch_rows, kRowThreads);
+  if (is_k333(kr))
+    subm_ranked_kernel<true><<<blocks, kRowThreads, 0, (cudaStream_t)stream>>>(
+        (const int4*)coords, n_ptr, cap, make_grid(grid, batch), kr, ws, map);
+  else
+    subm_ranked_kernel<false><<<blocks, kRowThreads, 0, (cudaStream_t)stream>>>(
+        (const int4*)coords, n_ptr, cap, make_grid(grid, batch), kr, ws, map);
   SPCONVB_LAUNCH_CHECK();
   return SPCONVB_OK;
 }
@@ -607,13 +632,21 @@ int spconvb_down_map_static(const int32_t* in_coords, const uint32_t* n_in_ptr, 
                             uint32_t* n_out_ptr, uint32_t cap_out, int32_t* map,
                             uint64_t* out_table, uint32_t out_slots, uint32_t flags,
                             uint32_t* status, void* stream) {
-  if (!in_grid || !ksize || !stride || !pad || !dilation) return SPCONVB_E_ARG;
+  // every argument check of spconvb_down_map that can fail comes first: nothing of the
+  // caller's memory (the optional output table) is cleared for a call that is then refused
+  if (!in_coords || !n_in_ptr || !in_grid || !ksize || !stride || !pad || !dilation ||
+      !out_coords || !n_out_ptr || !map)
+    return SPCONVB_E_ARG;
+  if (out_table && (out_slots < 2 || (out_slots & (out_slots - 1)) || out_slots < 2ull * cap_out))
+    return SPCONVB_E_ARG;
+  if (!grid_fits(in_grid, batch)) return SPCONVB_E_RANGE;
   int32_t og[3];
   for (int a = 0; a < 3; ++a) {
     if (ksize[a] < 1 || stride[a] < 1 || dilation[a] < 1 || pad[a] < 0) return SPCONVB_E_ARG;
     og[a] = spconvb_out_extent(in_grid[a], ksize[a], stride[a], pad[a], dilation[a]);
     if (og[a] < 1) return SPCONVB_E_ARG;
   }
+  if (ksize[0] * ksize[1] * ksize[2] > 65535) return SPCONVB_E_ARG;
   const size_t need = spconvb_down_workspace_bytes(og, batch);
   if (need == 0) return SPCONVB_E_RANGE;
   if (need > kStaticScratchBytes) return SPCONVB_E_SCRATCH_LIMIT;

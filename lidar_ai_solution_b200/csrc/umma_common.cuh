@@ -9,7 +9,8 @@ namespace spconvb {
 namespace umma_detail {
 
 constexpr int kChunk = 128;   // bytes of K per pipeline stage: one 128-byte swizzle atom per row
-constexpr int kMaxTaps = 27;  // taps whose neighbour indices are staged in shared memory
+constexpr int kMaxTaps = 27;  // most taps of a layer the tensor-core kernel takes
+constexpr int kMaxStages = 6; // deepest ring of gathered-row stages
 constexpr unsigned long long kWaitLimitNs = 250ull * 1000 * 1000;
 
 struct UmmaArgs {
@@ -23,12 +24,28 @@ struct UmmaArgs {
   const uint8_t* res;
   uint8_t* out;
   uint32_t* status;
+  const uint32_t* n_in_ptr;  // rows of `in` (for the L2 prefetch of input rows); may be null
+  uint32_t cap_in;           // rows the buffer of `in` holds
   int kvol;
-  int w_rep;       // copies of each weight chunk along the 128 accumulator lanes (1..128/Cout)
+  int w_rep;       // copies of each weight chunk along the accumulator rows: w_rep * Cout = 64 or 128
   int w_resident;  // 1: all chunks stay in shared memory for the whole launch; 0: streamed
+  int nstages;     // depth of the ring of gathered-row stages (2..kMaxStages)
+  int prefetch;    // tiles (per CTA) the L2 prefetch runs ahead of the gather; 0 = off
   int wait_test;   // > 0: producers withhold "stage full" from this chunk on (self-test)
   Epilogue ep;
 };
+
+// Shared-memory footprint of one launch configuration (the kernel carves it the same way).
+__host__ __device__ inline size_t umma_idx_bytes(int rb) {
+  const int opc = rb <= kChunk ? kChunk / rb : 1;  // taps per chunk
+  return (size_t)8 * 4 * opc * 36 * sizeof(int32_t);  // 8 warps x 4 slots x taps x (32 rows + pad)
+}
+__host__ __device__ inline size_t umma_smem_bytes(int rb, int cout, int nchunk, int w_rep,
+                                                  int w_resident, int nstages) {
+  const size_t wchunk = (size_t)w_rep * cout * kChunk;
+  const size_t w = w_resident ? (size_t)nchunk * wchunk : (size_t)nstages * wchunk;
+  return 1024 + w + (size_t)nstages * 256 * kChunk + umma_idx_bytes(rb) + 256;
+}
 
 // ------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -54,6 +71,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Non-blocking form: try_wait may hold the thread for a hardware-defined time before it
+// answers "not yet"; test_wait answers at once.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(bar), "r"(parity)
@@ -93,7 +123,12 @@ static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
                                           volatile uint32_t* abort_flag, uint32_t* status,
                                           uint32_t where) {
-  if (mbar_try_wait(bar, parity)) return true;
+  // Most waits end within a microsecond or two: they spin on the non-blocking test (a
+  // thread parked in try_wait wakes up late).  The clock is only read, and the thread only
+  // parked, when that was not enough.
+#pragma unroll 1
+  for (int i = 0; i < 256; ++i)
+    if (mbar_test_wait(bar, parity)) return true;
   return mbar_wait_slow(bar, parity, abort_flag, status, where);
 }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
@@ -101,12 +136,31 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32
                "r"(src_bytes)
                : "memory");
 }
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void st_shared_s32(uint32_t dst, int32_t v) {
+  asm volatile("st.shared.s32 [%0], %1;" ::"r"(dst), "r"(v) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() {
   asm volatile("cp.async.commit_group;" ::: "memory");
 }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+// The calling thread's earlier cp.async copies arrive on the barrier when they have landed
+// (the barrier's expected count includes this arrival: "noinc").
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+// Asks L2 to fetch a contiguous piece of global memory: address 16-byte aligned, size a
+// multiple of 16 bytes.  No data reaches the SM.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+  asm volatile("cp.async.wait_all;" ::: "memory");
 }
 __device__ __forceinline__ void fence_proxy_async() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

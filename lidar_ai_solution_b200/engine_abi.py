@@ -51,6 +51,8 @@ SYMBOLS = {
     "spconvb_engine_output": (C.c_int, [_VP, C.c_int, C.POINTER(_VP), _I64P, _I32P, _I32P, _I32P]),
     "spconvb_engine_output_layout": (C.c_int, [_VP, C.c_int, _I32P, _I64P, _I32P,
                                                C.POINTER(C.c_size_t)]),
+    "spconvb_engine_output_rows": (C.c_int, [_VP, C.c_int, C.POINTER(_VP), C.POINTER(_VP),
+                                             C.POINTER(C.c_uint32), _I32P, _I32P]),
     "spconvb_engine_tensor": (C.c_int, [_VP, _CP, C.POINTER(TensorView)]),
     "spconvb_engine_tensor_names": (_CP, [_VP]),
     "spconvb_engine_describe": (_CP, [_VP]),

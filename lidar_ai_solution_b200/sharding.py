@@ -40,3 +40,14 @@ def aggregate(elapsed_ms: float, frames_done: int, dist=None, device=None):
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     dist.all_reduce(f, op=dist.ReduceOp.SUM)
     return float(t.item()), int(f.item())
+
+
+def gather_floats(value: float, dist=None, device=None):
+    """[value of rank 0, value of rank 1, ...] on every rank (one element without a group)."""
+    if dist is None or not dist.is_initialized() or dist.get_world_size() == 1:
+        return [float(value)]
+    import torch
+    mine = torch.tensor([float(value)], dtype=torch.float64, device=device)
+    out = [torch.zeros_like(mine) for _ in range(dist.get_world_size())]
+    dist.all_gather(out, mine)
+    return [float(t.item()) for t in out]

@@ -56,6 +56,13 @@ def num_threads() -> int:
     return int(lib().orc_num_threads())
 
 
+def set_num_threads(n: int | None = None) -> int:
+    """OpenMP threads for the calls that follow; default: every CPU this process may run on."""
+    if n is None:
+        n = len(os.sched_getaffinity(0))
+    return int(lib().orc_set_num_threads(int(n)))
+
+
 def out_grid(grid, ksize, stride, pad, dil):
     return [int(lib().orc_out_extent(int(g), int(k), int(s), int(p), int(d)))
             for g, k, s, p, d in zip(grid, ksize, stride, pad, dil)]

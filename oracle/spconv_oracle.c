@@ -74,6 +74,19 @@ int orc_num_threads(void) {
 #endif
 }
 
+/* Sets the OpenMP team size of the calls that follow (launchers such as
+ * torch.distributed.run export OMP_NUM_THREADS=1, which would otherwise make
+ * the CPU baseline single-threaded).  Returns the size now in effect. */
+int orc_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+  return omp_get_max_threads();
+#else
+  (void)n;
+  return 1;
+#endif
+}
+
 /* ------------------------------------------------------------------------ */
 /* sorted key table: the oracle's coordinate lookup (no hashing on purpose). */
 

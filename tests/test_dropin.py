@@ -131,3 +131,40 @@ def test_cpp_interfaces_match_the_c_abi(tmp_path, mode):
         assert head[0] == 0x33FF1101 and head[1] == 4 and head[2] == 2
         got = np.frombuffer(raw[12 + 16:], np.float16).reshape(want.shape)
     assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dds", [False, True])
+def test_sparse_output_through_the_cpp_interface(tmp_path, dds):
+    """A graph whose output is a sparse tensor (EngineBuilder::push_output on a convolution,
+    engine.hpp:158): output(0) carries features, indices, grid and the device-side row count,
+    and reports the input's row count when the host knows it."""
+    import torch
+    from lidar_ai_solution_b200 import engine
+    grid = (41, 360, 360)
+    n = 5000
+    coords = scenes.make_coords(n, grid, 9)
+    feats = scenes.make_point_features(coords, 9)
+    model = models.single_layer(5, 16, seed=9, output_bound=8000)
+    onnx = str(tmp_path / "layer.onnx")
+    onnx_writer.save(model, onnx)
+    e = engine.Engine.from_onnx(onnx, engine.PRECISION_FP16)
+    e.forward(torch.from_numpy(feats).cuda(), torch.from_numpy(coords).cuda(), grid)
+    torch.cuda.synchronize()
+    want = e.output(0)[:n].cpu().numpy()
+    exe = _compile_driver(tmp_path, v10=False)
+    _write_tensor(str(tmp_path / "f.tensor"), feats)
+    _write_tensor(str(tmp_path / "i.tensor"), coords)
+    out = str(tmp_path / "out.tensor")
+    args = [exe, onnx, "fp16", str(tmp_path / "f.tensor"), str(tmp_path / "i.tensor"),
+            *map(str, grid), out] + (["dds"] if dds else [])
+    r = subprocess.run(args, capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    rows = 8000 if dds else n   # the capacity when only the device knows the count
+    assert "sparse output: indices %d x 4, rows on device %d, grid 41 360 360" % (rows, n) in r.stdout, \
+        r.stdout
+    raw = open(out, "rb").read()
+    head = np.frombuffer(raw[:12 + 8], np.int32)
+    assert head[0] == 0x33FF1101 and head[1] == 2 and tuple(head[3:5]) == (rows, 16)
+    got = np.frombuffer(raw[12 + 8:], np.float16).reshape(rows, 16)
+    assert np.array_equal(got[:n].view(np.uint16), want.view(np.uint16))

@@ -57,9 +57,15 @@ def _compare_all(e, T, exact):
             assert np.array_equal(got["coords"][:n].cpu().numpy(), ref["coords"])
         g = got["features"][:n].cpu().numpy()
         assert g.dtype == ref["feat"].dtype, "tensor %s stored as %s" % (tid, g.dtype)
-        if exact or g.dtype == np.int8:
-            if exact:
-                assert np.array_equal(g.view(np.uint8), ref["feat"].view(np.uint8)), tid
+        if exact:
+            assert np.array_equal(g.view(np.uint8), ref["feat"].view(np.uint8)), tid
+        elif g.dtype == np.int8:
+            # int8 tensors downstream of tensor-core fp16 layers: a rounding may flip where the
+            # fp32 sums were formed in another order, so they are held to 1 LSB on all but a
+            # small share of the elements (the exact per-layer check is _replay_layers)
+            d = np.abs(g.astype(np.int32) - ref["feat"].astype(np.int32))
+            assert float(np.mean(d > 1)) <= 0.05, "tensor %s: %g of the elements differ by > 1 LSB" \
+                % (tid, float(np.mean(d > 1)))
         else:
             r = ref["feat"].astype(np.float32)
             err = float(np.abs(g.astype(np.float32) - r).max()) / max(float(np.abs(r).max()), 1e-6)
@@ -155,10 +161,12 @@ def test_dense_output_layouts_through_the_engine(kind, layout, int8_out, tmp_pat
         assert np.count_nonzero(got) > 0
 
 
-def _replay_layers(model, e, precision, in_coords):
+def _replay_layers(model, e, precision, in_coords, stats=None):
     """Per-layer parity on the tensor-core path: every conv (+Add+Relu) is re-run on the
     oracle from the engine's own input tensors; int8 results must be identical, fp16 within
-    1e-2 of the layer's absmax."""
+    1e-2 of the layer's absmax.  `stats` (a list) receives, per fp16 layer, the share of
+    elements whose error exceeds 1e-2 of their own magnitude (with an absolute floor of 1e-2
+    of the layer's absmax under it), the per-element reading of "1e-2 relative"."""
     kind, dr = graph_oracle.resolve(model, precision)
     nodes = model["nodes"]
     checked = 0
@@ -184,7 +192,10 @@ def _replay_layers(model, e, precision, in_coords):
             r = ref.astype(np.float32)
             scale = max(float(np.abs(r).max()), 1e-6)
             lim = 1.0 if g.dtype == np.int8 else 1e-2 * scale
-            assert float(np.abs(g.astype(np.float32) - r).max()) <= lim, n["name"]
+            err = np.abs(g.astype(np.float32) - r)
+            assert float(err.max()) <= lim, n["name"]
+            if stats is not None and g.dtype != np.int8:
+                stats.append((n["name"], float(np.mean(err > 1e-2 * np.maximum(np.abs(r), 1e-2 * scale)))))
         checked += 1
     return checked
 
@@ -403,6 +414,120 @@ def test_reference_frame_full_size_int8(golden_dir):
     torch.cuda.synchronize()
     assert exact.status()[0] == 0
     assert np.array_equal(exact.output(0).cpu().numpy().view(np.uint16), outs[0].view(np.uint16))
+
+
+# ------------------------------------------------ benchmark sizes, tensor-core path
+BENCH_GRID = (41, 1440, 1440)
+
+
+@pytest.mark.parametrize("kind,precision,voxels,seed", [
+    ("centerpoint", "int8", 120000, 1000),   # the frame bench.py times first (rank 0, seed 1000)
+    ("centerpoint", "int8", 200000, 163),    # the upper end of the mixed-size set
+    ("bevfusion", "fp16", 60000, 7),
+    ("bevfusion", "fp16", 200000, 8),
+])
+def test_per_layer_parity_at_benchmark_sizes(kind, precision, voxels, seed):
+    """The per-layer replay of _replay_layers at the sizes the benchmark runs: full
+    41x1440x1440 grid, 60 k - 200 k voxels (235 k - 400 k rows after the first strided conv),
+    the benchmark's output bounds, tensor-core kernels.  int8 layers identical to the oracle,
+    fp16 layers within 1e-2 of the layer's absmax, and at most 0.1 % of an fp16 layer's
+    elements further than 1e-2 from the oracle relative to their own magnitude."""
+    eng = _engine_mod()
+    coords = scenes.make_coords(voxels, BENCH_GRID, seed)
+    feats = scenes.make_point_features(coords, seed)
+    bound = 300000 if voxels <= 120000 else 520000
+    model = models.scn_backbone(kind, seed=0, grid_zyx=BENCH_GRID, output_bound=bound)
+    if precision == "int8":
+        c0 = scenes.make_coords(120000, BENCH_GRID, 0)
+        f0 = scenes.make_point_features(c0, 0)
+        model = models.quantize(model, eng.calibrate(model, _dev(f0), _dev(c0), BENCH_GRID))
+    p = eng.PRECISION_INT8 if precision == "int8" else eng.PRECISION_FP16
+    e = eng.Engine.from_model(model, p, eng.BUILD_KEEP_TENSORS | eng.BUILD_NO_FUSION)
+    e.forward(_dev(feats), _dev(coords), BENCH_GRID)
+    torch.cuda.synchronize()
+    assert e.status()[0] == 0
+    stats = []
+    n_conv = sum(1 for n in model["nodes"] if n["op"] == "conv")
+    assert _replay_layers(model, e, precision, coords, stats) == n_conv
+    for name, share in stats:
+        assert share <= 1e-3, "%s: %g of the elements beyond 1e-2 relative" % (name, share)
+    e.close()
+
+
+def test_batched_forward_equals_frame_by_frame():
+    """Several frames in one engine call (told apart by the batch column of the indices) give,
+    frame for frame, the bits of single-frame calls: dense output slices and every stage's rows.
+    The reference engine takes one frame per call (engine.hpp:63-71); the batch dimension is
+    this library's way of letting the tiles of several frames share a kernel launch."""
+    eng = _engine_mod()
+    sizes = [(9000, 11), (3000, 12), (12000, 13), (1, 14)]
+    frames = [_frame(n, seed=s) for n, s in sizes]
+    model = _quantized("centerpoint", *frames[0], seed=11)
+    one = eng.Engine.from_model(model, eng.PRECISION_INT8, 0)
+    want = []
+    for f, c in frames:
+        one.forward(_dev(f), _dev(c), GRID)
+        torch.cuda.synchronize()
+        assert one.status()[0] == 0
+        want.append(one.output(0).clone())
+    B = len(frames)
+    feats = np.concatenate([f for f, _ in frames])
+    coords = np.concatenate([np.concatenate([np.full((len(c), 1), b, np.int32), c[:, 1:]], 1)
+                             for b, (_, c) in enumerate(frames)])
+    many = eng.Engine.from_model(model, eng.PRECISION_INT8, 0)
+    many.prepare(GRID, B)
+    many.forward(_dev(feats), _dev(coords), GRID, batch=B)
+    torch.cuda.synchronize()
+    assert many.status()[0] == 0
+    got = many.output(0)
+    assert got.shape[0] == B and tuple(got.shape[1:]) == tuple(want[0].shape[1:])
+    for b in range(B):
+        assert torch.equal(got[b], want[b][0]), "frame %d" % b
+    # the same through a captured graph with the row count on the device, frames in another order
+    order = [2, 0, 3, 1]
+    feats2 = np.concatenate([frames[i][0] for i in order])
+    coords2 = np.concatenate([np.concatenate([np.full((len(frames[i][1]), 1), b, np.int32),
+                                              frames[i][1][:, 1:]], 1)
+                              for b, i in enumerate(order)])
+    df, dc = _dev(feats2), _dev(coords2)
+    n_dev = torch.tensor([len(feats2)], dtype=torch.int32, device="cuda")
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        many.forward_dds(df, dc, n_dev, GRID, batch=B, stream=stream)
+        stream.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            many.forward_dds(df, dc, n_dev, GRID, batch=B, stream=stream)
+        g.replay()
+    torch.cuda.synchronize()
+    assert many.status()[0] == 0
+    got = many.output(0)
+    for b, i in enumerate(order):
+        assert torch.equal(got[b], want[i][0]), "frame %d in slot %d" % (i, b)
+
+
+def test_row_count_beyond_the_buffers_sets_status_and_touches_nothing_else():
+    """DDS with a device-side row count larger than the caller's buffers: every kernel clamps
+    to the capacity it was given, the overflow bit is set, and memory behind the feature rows
+    the engine was allowed to write keeps its pattern."""
+    eng = _engine_mod()
+    from lidar_ai_solution_b200 import cabi
+    cap = 6000
+    feats, coords = _frame(cap, seed=21)
+    model = _quantized("centerpoint", feats, coords, seed=21)
+    e = eng.Engine.from_model(model, eng.PRECISION_INT8, eng.BUILD_KEEP_TENSORS)
+    df, dc = _dev(feats), _dev(coords)
+    n_dev = torch.tensor([cap], dtype=torch.int32, device="cuda")
+    e.forward_dds(df, dc, n_dev, GRID)
+    torch.cuda.synchronize()
+    assert e.status()[0] == 0
+    want = e.output(0).clone()
+    n_dev.fill_(5 * cap + 7)   # a count the buffers do not hold
+    e.forward_dds(df, dc, n_dev, GRID)
+    torch.cuda.synchronize()
+    st = e.status()
+    assert st[0] & cabi.ST_OVERFLOW
+    assert torch.equal(e.output(0), want)   # the first `cap` rows were processed, nothing more
 
 
 # ------------------------------------------------------------ pyscn binding, infer CLI

@@ -57,6 +57,28 @@ def test_host_side_size_helpers_need_no_gpu():
     assert lib.spconvb_conv_packed_bytes(cabi.I8, 16, 16, 27) == 4 * 16 * 128
 
 
+def test_argument_checks_come_before_any_device_work():
+    """Calls that are refused for their arguments return before the first CUDA call, so they
+    can be checked without a GPU: the allocation-free strided rulebook refuses null buffers, an
+    output table that is not a power of two or too small, and grids beyond its scratch area;
+    the elementwise entry points refuse a zero capacity."""
+    cabi, lib = _lib()
+    g, k, s, p, d = (cabi.i3(v) for v in ((21, 64, 64), (3, 3, 3), (2, 2, 2), (1, 1, 1), (1, 1, 1)))
+    fake = 0x1000  # never dereferenced: every call below is refused first
+
+    def static(coords=fake, out_coords=fake, table=None, slots=0, grid=g, cap_out=1000, s=s):
+        return lib.spconvb_down_map_static(coords, fake, 1000, 0, grid, 1, k, s, p, d, None, 0,
+                                           out_coords, fake, cap_out, fake, table, slots, 0, None,
+                                           None)
+    assert static(coords=None) == -1 and static(out_coords=None) == -1       # SPCONVB_E_ARG
+    assert static(table=fake, slots=3000) == -1      # not a power of two
+    assert static(table=fake, slots=1024) == -1      # fewer than 2 * cap_out slots
+    # stride 1 keeps 85 M output cells: far beyond the scratch area
+    assert static(grid=cabi.i3((41, 1440, 1440)), s=cabi.i3((1, 1, 1))) == cabi.E_SCRATCH_LIMIT
+    assert lib.spconvb_relu(fake, cabi.I8, 16, fake, 0, fake, None) == -1
+    assert lib.spconvb_convert(fake, cabi.F16, 5, cabi.F16, 4, 1.0, fake, 100, fake, None) == -1
+
+
 def test_weight_packing_layout():
     """Chunk j, row n, 16-byte segment c is stored at segment c ^ (n % 8) of row n."""
     cabi, lib = _lib()

@@ -153,7 +153,7 @@ def test_down_map_overflow_sets_status():
 
 
 # --------------------------------------------------------------- convolutions
-def _int8_layer(n, c_in, c_out, seed, simt, out_kind, grid=(41, 180, 180)):
+def _int8_layer(n, c_in, c_out, seed, simt, out_kind, grid=(41, 180, 180), hint=False):
     ops = _ops()
     pb = int8_problem(n, c_in, c_out, grid, seed)
     m_ref, _ = orc.subm_map(pb["coords"], grid)
@@ -166,7 +166,7 @@ def _int8_layer(n, c_in, c_out, seed, simt, out_kind, grid=(41, 180, 180)):
     wts = ops.ConvWeights(pb["wq"], ops.I8, pb["scale"], pb["bias"])
     out = ops.conv_forward(_dev(pb["xq"]), _dev(m_ref), n_ptr, wts, act=ops.ACT_RELU,
                            out_kind=out_kind, inv_out_scale=float(inv_out), force_simt=simt,
-                           status=st)
+                           status=st, n_in_ptr=n_ptr if hint else None)
     torch.cuda.synchronize()
     _status_ok(st)
     return out.cpu().numpy(), ref
@@ -178,6 +178,17 @@ def test_conv_int8_bit_exact(c, simt):
     """int8 x int8 -> int32 is exact, the epilogue is defined operation by operation,
     so the requantised int8 output must be identical (tolerance 0 LSB)."""
     got, ref = _int8_layer(3000 if simt else 10000, c, c, seed=c, simt=simt, out_kind=orc.KIND_I8)
+    assert got.dtype == np.int8 and np.array_equal(got, ref)
+
+
+@pytest.mark.parametrize("c", [16, 32, 64, 128])
+@pytest.mark.parametrize("n", [120000, 200000])
+def test_conv_int8_bit_exact_at_benchmark_sizes(c, n):
+    """The layer sweep of the benchmark configurations: SubM 3x3x3, Cin = Cout = c, on the
+    41x1440x1440 grid with 120 k and 200 k voxels (many tiles per CTA, balanced tile heights,
+    the L2 prefetch running ahead of the gather): identical to the oracle."""
+    got, ref = _int8_layer(n, c, c, seed=c + n, simt=False, out_kind=orc.KIND_I8,
+                           grid=(41, 1440, 1440), hint=True)
     assert got.dtype == np.int8 and np.array_equal(got, ref)
 
 
