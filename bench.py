@@ -576,10 +576,10 @@ def time_launches(torch, fn, reps, flush):
 
 
 def from_points_leg(torch, dev, onnx_path, precision, steps):
-    """H2D of a raw 300 000-point sweep -> voxelizer -> backbone -> D2H of the BEV tensor, one
+    """H2D of a raw 140 000-point sweep -> voxelizer -> backbone -> D2H of the BEV tensor, one
     frame at a time on one stream (the call sequence of CenterPoint::doinfer up to the RPN)."""
     from lidar_ai_solution_b200 import cabi, engine, scenes
-    n_points = 300000
+    n_points = 140000
     host_pts = torch.from_numpy(scenes.make_points(n_points, 7)).pin_memory()
     dev_pts = torch.empty_like(host_pts, device=dev)
     run, bufs = make_voxelizer(torch, n_points, False)

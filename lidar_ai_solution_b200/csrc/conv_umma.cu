@@ -64,17 +64,18 @@ static int env_int(const char* name, int fallback) {
   return atoi(v);
 }
 
-static bool config_fits(int rb, int cout, int nchunk, int rep, int resident, int stages,
-                        size_t* smem) {
-  *smem = umma_smem_bytes(rb, cout, nchunk, rep, resident, stages);
+static bool config_fits(int cout, int nchunk, int rep, int resident, int stages, size_t* smem) {
+  *smem = umma_smem_bytes(cout, nchunk, rep, resident, stages);
   return *smem <= 232448;
 }
 
-// Residency removes the weight chunk from every stage (as much L2 traffic and shared-memory
-// writing as half the gathered rows), so it is preferred whenever it leaves at least three
-// stages.  128 accumulator rows (the most copies) come first: with 64 rows half the lanes of
-// every epilogue warp carry nothing, and the epilogue of a tile must not outlast the next
-// tile's main loop.
+// Measured on the B200 (layer sweep, 200 k - 1 M rows, every channel width): streaming the
+// weight chunk with every stage, copied to all 128 accumulator rows, is as fast as or faster
+// than keeping the weights resident, because it leaves the deepest ring of row stages and
+// lets all lanes of the 8 epilogue warps work (with 64 accumulator rows half of them carry
+// nothing, and the epilogue of a tile then outlasts the next tile's main loop).  The weight
+// chunk comes from L2 by one bulk copy per stage and costs no producer instructions.  So:
+// stream with the most copies; resident configurations remain for the overrides.
 static UmmaConfig choose_config(int rb, int cout, int kvol) {
   static const int force_m = env_int("SPCONVB_CONV_M", 0);
   static const int force_res = env_int("SPCONVB_CONV_RESIDENT", -1);
@@ -86,12 +87,12 @@ static UmmaConfig choose_config(int rb, int cout, int kvol) {
     size_t smem;
     int st = 0;
     for (int n = 2; n <= kMaxStages; ++n)
-      if (config_fits(rb, cout, nchunk, rep, resident, n, &smem)) st = n;
+      if (config_fits(cout, nchunk, rep, resident, n, &smem)) st = n;
     if (force_stages >= 2 && force_stages <= st) st = force_stages;
     return st;
   };
   struct Cand { int rep, resident, need; };
-  Cand order[4] = {{full, 1, 3}, {half, 1, 3}, {full, 0, 2}, {half, 0, 2}};
+  Cand order[4] = {{full, 0, 2}, {half, 0, 2}, {full, 1, 2}, {half, 1, 2}};
   UmmaConfig c{};
   for (const Cand& o : order) {
     if (o.rep < 1) continue;
@@ -111,7 +112,7 @@ static UmmaConfig choose_config(int rb, int cout, int kvol) {
     c.nstages = best_stages(full, 0);
   }
   c.prefetch = prefetch < 0 ? 0 : (prefetch > 8 ? 8 : prefetch);
-  c.smem = umma_smem_bytes(rb, cout, nchunk, c.w_rep, c.w_resident, c.nstages);
+  c.smem = umma_smem_bytes(cout, nchunk, c.w_rep, c.w_resident, c.nstages);
   return c;
 }
 

@@ -26,14 +26,17 @@
 //               contiguous bytes of one output row per lane
 //   warp  8     allocates TMEM; one lane issues tcgen05.mma (kind::i8 with int32
 //               accumulators or kind::f16 with fp32 accumulators)
-//   warps 9-16  producers: each warp owns 32 rows of the tile.  Neighbour indices
-//               travel chunk by chunk: 4-byte cp.async copies, two chunks ahead,
-//               straight into a small per-warp ring in shared memory (no register
-//               staging, nothing to stall on), from where the gathering threads
-//               take eight at a time.
-//               Rows are gathered with 16-byte cp.async (8 lanes per row, so a row
-//               is one contiguous request; zero-fill for missing neighbours)
-//               straight into the 128-byte-swizzled K-major layout the MMA reads.
+//   warps 9-24  producers, two groups of 8 warps that take the chunks in turn (the
+//               work of a warp per chunk is a chain of dependent steps - wait for
+//               the stage, neighbour indices, addresses, copies, arrival - that
+//               takes longer than the tensor pipe needs for the chunk; two groups
+//               give each warp two chunk periods for it).  Within a group each warp
+//               owns 32 rows of the tile.  A thread loads the 8 neighbour indices
+//               it needs for its next chunk straight into registers (two 16-byte
+//               loads, a round ahead) and gathers with 16-byte cp.async (8 lanes
+//               per row, so a row is one contiguous request; zero-fill for missing
+//               neighbours) straight into the 128-byte-swizzled K-major layout the
+//               MMA reads.
 //               A producer never waits for its copies: every thread lets them
 //               arrive on the stage's mbarrier when they land, so all free stages
 //               of the ring are in flight.  One thread also streams the
@@ -56,9 +59,7 @@
 // build, never the shipped one): one lane of a producer warp, the MMA thread and one
 // epilogue lane add up the clock cycles they spend in each part of their loops, per CTA;
 // spconvb_debug_conv_profile() copies the table out.  In that build a negative
-// spconvb_conv_params.wait_test -f switches work off: f & 1 no gather copies, f & 2 no MMAs,
-// f & 4 no index copies, f & 8 one "stage full" arrival per producer warp instead of one per
-// thread (4 and 8 also switch the gather copies off: they would be wrong with them).
+// spconvb_conv_params.wait_test -f switches work off: f & 1 no gather copies, f & 2 no MMAs.
 #ifdef SPCONVB_CONV_PROFILE
 #define PROF(...) __VA_ARGS__
 #else
@@ -78,11 +79,9 @@ constexpr int kRowsBytes = kTileRows * kChunk;  // gathered rows of one stage
 constexpr int kEpiWarps = 8;
 constexpr int kMmaWarp = 8;
 constexpr int kProdWarp0 = 9;
-constexpr int kProdThreads = 256;
+constexpr int kProdThreads = 512;   // two groups of 8 producer warps
 constexpr int kCtaThreads = 32 * kProdWarp0 + kProdThreads;
 constexpr uint32_t kTmemCols = 2 * kTileRows;
-constexpr int kIdxTapStride = 36;  // words between taps in the index ring (32 rows + padding
-                                   // that spreads the taps of a 16-byte read over all banks)
 constexpr size_t kMaxSmem = 232448;  // 227 KB: the most dynamic shared memory of a CTA
 
 // 32-bit instruction descriptor: [4,6) D format (1 = f32, 2 = s32), [7,10) A
@@ -143,7 +142,6 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
   constexpr int OPC = RB <= kChunk ? kChunk / RB : 1;   // taps per chunk
   constexpr int SPO = RB <= kChunk ? RB / 16 : 8;       // 16-byte segments per tap per chunk
   constexpr int CPT = RB <= kChunk ? 1 : RB / kChunk;   // chunks per tap
-  constexpr int kIdxSlot = OPC * kIdxTapStride;         // words of one ring slot of one warp
 
   const int kbytes = a.kvol * RB;
   const int nchunk = (kbytes + kChunk - 1) / kChunk;
@@ -155,14 +153,13 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
   const uint32_t nst = (uint32_t)a.nstages;
 
   // Shared memory: the weights (all chunks, or one per stage), the gathered-row stages,
-  // the producers' index rings, the barriers.
+  // the barriers.
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
   uint8_t* sW = smem;
   uint8_t* sR = sW + (w_resident ? (uint32_t)nchunk : nst) * w_chunk_smem;
-  int32_t* sIdx = (int32_t*)(sR + nst * kRowsBytes);
-  uint64_t* bars = (uint64_t*)((uint8_t*)sIdx + umma_idx_bytes(RB));
+  uint64_t* bars = (uint64_t*)(sR + nst * kRowsBytes);
   uint32_t* tmem_holder = (uint32_t*)(bars + 2 * kMaxStages + 5);
   volatile uint32_t* abort_flag = tmem_holder + 1;
 
@@ -177,8 +174,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kMaxStages; ++s) {
-      mbar_init(bar_full + 8 * s, kProdThreads + 1);  // every producer thread + the weights
-      PROF(if (a.wait_test < 0 && ((-a.wait_test) & 8)) mbar_init(bar_full + 8 * s, 9);)
+      mbar_init(bar_full + 8 * s, kProdThreads / 2 + 1);  // a group's threads + the weights
       mbar_init(bar_empty + 8 * s, 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -215,14 +211,17 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
 
   if (warp >= kProdWarp0) {
     // ------------------------------------------------------------ producers
-    // A chunk of the row tile is 256 rows x 8 segments of 16 bytes = 2048 copies,
-    // 8 per producer thread.  Producer warp w owns rows 32w..32w+31; a thread copies
-    // segment `seg` of rows 32w + 8 slot + i, i = 0..7 (8 lanes per row, so the lanes
-    // that read the same neighbour row ask for one contiguous piece of it).  The code
-    // is branch-free (missing neighbours are zero-filled copies) so the address
-    // arithmetic and the copies of the 8 items overlap.
-    const uint32_t pw = (uint32_t)warp - kProdWarp0;
-    const uint32_t r = threadIdx.x - kProdWarp0 * 32;  // thread 0 also copies the weights
+    // Two groups of 8 warps take the chunks in turn (group g the chunks g, g + 2, ...), so a
+    // warp has two chunk periods for the round trip of one chunk: wait for the stage, look
+    // up the neighbours, issue the copies.  Within a group, warp w owns rows 32w..32w+31 of
+    // the tile.  A chunk of the row tile is 256 rows x 8 segments of 16 bytes = 2048 copies,
+    // 8 per thread: a thread copies segment `seg` of rows 32w + 8 slot + i, i = 0..7 (8
+    // lanes per row, so the lanes that read the same neighbour row ask for one contiguous
+    // piece of it).  Missing neighbours are zero-filled copies, so the 8 items are
+    // branch-free and their address arithmetic and copies overlap.
+    const uint32_t pw_all = (uint32_t)warp - kProdWarp0;
+    const uint32_t grp = pw_all >> 3, pw = pw_all & 7u;
+    const bool w_thread = pw == 0u && lane == 0u;  // also streams the weights of its chunks
     const uint32_t seg = lane & 7u;        // 16-byte segment of the chunk this thread copies
     const uint32_t slot = lane >> 3;       // its 8 rows of the warp's 32
     // row R of the tile lives at (R / 8) * 1024 + (R % 8) * 128, its segments XOR-ed
@@ -232,34 +231,27 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
     const uint32_t seg_tap = RB <= kChunk ? seg / SPO : 0u;
     const uint32_t seg_byte = RB <= kChunk ? (seg % SPO) * 16u : seg * 16u;
     const bool has_rows = pw * 32u < tile_rows;  // else this warp only keeps the barriers going
-    int32_t* wring = sIdx + pw * (4 * kIdxSlot);
+    const uint32_t row_in_tile = pw * 32u + slot * 8u;
+    // 16-byte index loads need the map rows 16-byte aligned and whole groups of 8 inside them
+    const bool vec_ok = (a.cap & 7u) == 0u && ((uintptr_t)a.map & 15u) == 0u;
 
-    // Indices of one chunk: lane l copies the chunk's taps of row 32w + l (coalesced) into a
-    // slot of the warp's ring; taps past the kernel and rows past the end get -1.
-    auto issue_idx = [&](uint32_t tile, int j, uint32_t ring_slot) {
-      PROF(if (a.wait_test < 0 && ((-a.wait_test) & 4)) return;)
-      const uint32_t row = tile * tile_rows + pw * 32u + lane;
-      const bool valid = has_rows && tile < ntiles && row < n_out;
-      const int k0 = RB <= kChunk ? j * OPC : j / CPT;
-      const int32_t* src = a.map + (size_t)k0 * a.cap + row;
-      const uint32_t dst = smem_u32(wring + ring_slot * kIdxSlot + lane);
+    // The 8 neighbour indices this thread needs for chunk j of a tile: its tap's map entries
+    // of its 8 rows, straight from global memory into registers (two 16-byte loads; the 8
+    // lanes of a row group that share a tap read the same 32 bytes).  Rows past the end,
+    // taps past the kernel and tiles past the last give -1.
+    auto load_idx = [&](uint32_t tile, int j, int32_t (&v)[8]) {
+      const int k = RB <= kChunk ? j * OPC + (int)seg_tap : j / CPT;
+      const uint32_t row = tile * tile_rows + row_in_tile;
+      const bool live = has_rows && tile < ntiles && k < a.kvol && row < n_out;
+      const int32_t* src = a.map + (size_t)k * a.cap + row;
+      if (live && vec_ok && row + 8u <= n_out) {
+        const int4 lo = __ldg((const int4*)src), hi = __ldg((const int4*)src + 1);
+        v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w;
+        v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+      } else {
 #pragma unroll
-      for (int t = 0; t < OPC; ++t) {
-        if (valid && k0 + t < a.kvol) cp_async4(dst + t * (kIdxTapStride * 4), src + (size_t)t * a.cap);
-        else st_shared_s32(dst + t * (kIdxTapStride * 4), -1);
+        for (uint32_t i = 0; i < 8; ++i) v[i] = (live && row + i < n_out) ? __ldg(src + i) : -1;
       }
-    };
-    auto advance = [&](uint32_t& tile, int& j) {
-      if (++j == nchunk) {
-        j = 0;
-        tile += gridDim.x;
-      }
-    };
-    // mbarrier traffic is kept per warp: one lane polls and broadcasts.
-    auto warp_wait = [&](uint32_t bar, uint32_t parity, uint32_t where) -> bool {
-      uint32_t ok = 1u;
-      if (lane == 0) ok = mbar_wait(bar, parity, abort_flag, a.status, where) ? 1u : 0u;
-      return __shfl_sync(0xffffffffu, ok, 0) != 0u;
     };
     // L2 prefetch of what tile `pt` will read: its map lines (lanes 0-3 of every warp take
     // the taps w, w+8, ...), its share of the input rows and its residual rows.  Bulk
@@ -290,9 +282,10 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
         }
       }
     };
-    for (int p = 0; p < a.prefetch; ++p) prefetch_tile(blockIdx.x + (uint32_t)p * gridDim.x);
+    if (grp == 0u)
+      for (int p = 0; p < a.prefetch; ++p) prefetch_tile(blockIdx.x + (uint32_t)p * gridDim.x);
 
-    if (r == 0 && w_resident && blockIdx.x < ntiles) {
+    if (grp == 0u && w_thread && w_resident && blockIdx.x < ntiles) {
       mbar_expect_tx(bar_w, (uint32_t)nchunk * w_chunk_smem);
       for (int j = 0; j < nchunk; ++j)
         for (uint32_t c = 0; c < w_rep; ++c)
@@ -300,77 +293,77 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
                    a.wpk + (size_t)j * (COUT * kChunk), COUT * kChunk, bar_w);
     }
 
-    uint32_t g_tile = blockIdx.x, l_tile = blockIdx.x;  // gather and index-copy cursors
-    int g_j = 0, l_j = 0;
-    // The index ring (4 slots) runs three chunks ahead.  Every round commits one cp.async
-    // group: its row copies and, issued after them, the index copies of the chunk three
-    // rounds on.  The "stage full" arrival of a round therefore never waits for index copies
-    // issued in the same round, and the wait at the top of a round (all but the two newest
-    // groups) covers this round's indices while leaving two chunks of rows in flight.
-    for (uint32_t p = 0; p < 3; ++p) {
-      issue_idx(l_tile, l_j, p);
-      advance(l_tile, l_j);
-      cp_async_commit();
-    }
-    uint32_t it = 0, s = 0, ph = 0, rs = 0;
-    bool alive = true;
-    PROF(long long p_idx = 0, p_wait = 0, p_issue = 0, p_t0 = clock64(), t_a, t_b;)
-    PROF(const bool no_copies = a.wait_test < 0 && ((-a.wait_test) & 13);)
-    PROF(const bool warp_arrive = a.wait_test < 0 && ((-a.wait_test) & 8);)
-    while (g_tile < ntiles) {
-      PROF(t_a = clock64();)
-      cp_async_wait<2>();
-      __syncwarp();
-      if (g_j == 0 && a.prefetch > 0) prefetch_tile(g_tile + (uint32_t)a.prefetch * gridDim.x);
-      PROF(t_b = clock64(); p_idx += t_b - t_a;)
-      if (!warp_wait(bar_empty + 8 * s, ph ^ 1u, 1u)) {
-        alive = false;
-        break;
+    // This group's chunks: numbers it = grp, grp + 2, ... of the CTA's chunk sequence (tile
+    // after tile, nchunk chunks each); chunk `it` uses stage it % nst.
+    auto advance2 = [&](uint32_t& tile, int& j) {  // two chunks on
+      j += 2;
+      while (j >= nchunk) {
+        j -= nchunk;
+        tile += gridDim.x;
       }
+    };
+    uint32_t tile = blockIdx.x;
+    int j = 0;
+    if (grp == 1u) {
+      j = 1;
+      while (j >= nchunk) {
+        j -= nchunk;
+        tile += gridDim.x;
+      }
+    }
+    uint32_t it = grp, s = grp % nst, ph = (grp / nst) & 1u;
+    int32_t cur[8], nxt[8];
+    load_idx(tile, j, cur);
+    PROF(long long p_idx = 0, p_wait = 0, p_issue = 0, p_t0 = clock64(), t_a, t_b; uint32_t p_n = 0;)
+    PROF(const bool no_copies = a.wait_test < 0 && ((-a.wait_test) & 1);)
+    while (tile < ntiles) {
+      PROF(t_a = clock64();)
+      uint32_t ntile = tile;
+      int nj = j;
+      advance2(ntile, nj);
+      load_idx(ntile, nj, nxt);  // used a round from now
+      if (j == 0 && a.prefetch > 0) prefetch_tile(tile + (uint32_t)a.prefetch * gridDim.x);
+      PROF(t_b = clock64(); p_idx += t_b - t_a;)
+      // every lane polls: one shared-memory word, no divergence, no broadcast afterwards
+      if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, a.status, 1u)) break;
       PROF(t_a = clock64(); p_wait += t_a - t_b;)
-      if (r == 0) {
+      if (w_thread) {
         if (w_resident) {
           mbar_arrive(bar_full + 8 * s);
         } else {
           mbar_expect_tx(bar_full + 8 * s, w_chunk_smem);
           for (uint32_t c = 0; c < w_rep; ++c)
             bulk_g2s(smem_u32(sW + s * w_chunk_smem + c * (COUT * kChunk)),
-                     a.wpk + (size_t)g_j * (COUT * kChunk), COUT * kChunk, bar_full + 8 * s);
+                     a.wpk + (size_t)j * (COUT * kChunk), COUT * kChunk, bar_full + 8 * s);
         }
       }
       if (has_rows PROF(&& !no_copies)) {
-        const uint32_t byte = seg_byte + (RB > kChunk ? (uint32_t)(g_j % CPT) * kChunk : 0u);
-        const int4* idx_k =
-            (const int4*)(wring + rs * kIdxSlot + seg_tap * kIdxTapStride + slot * 8u);
-        const int4 ia = idx_k[0], ib = idx_k[1];
-        const int32_t src_row[8] = {ia.x, ia.y, ia.z, ia.w, ib.x, ib.y, ib.z, ib.w};
+        const uint32_t byte = seg_byte + (RB > kChunk ? (uint32_t)(j % CPT) * kChunk : 0u);
         const uint32_t stage_addr = smem_u32(sR + s * kRowsBytes) + dst_base;
 #pragma unroll
         for (uint32_t i = 0; i < 8; ++i) {
-          const int32_t sr = src_row[i];
+          const int32_t sr = cur[i];
           cp_async16(stage_addr + i * 128u + ((seg ^ i) << 4),
                      a.in + (size_t)(sr < 0 ? 0 : sr) * RB + byte, sr < 0 ? 0u : 16u);
         }
       }
-      PROF(if (warp_arrive) { if (lane == 0) mbar_arrive(bar_full + 8 * s); } else)
       if (!(a.wait_test > 0 && it + 1u >= (uint32_t)a.wait_test))
         cp_async_arrive_noinc(bar_full + 8 * s);
-      issue_idx(l_tile, l_j, (rs + 3u) & 3u);
-      advance(l_tile, l_j);
-      cp_async_commit();
-      advance(g_tile, g_j);
-      ++it;
-      rs = (rs + 1u) & 3u;
-      if (++s == nst) {
-        s = 0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) cur[i] = nxt[i];
+      tile = ntile;
+      j = nj;
+      it += 2;
+      s += 2;
+      if (s >= nst) {
+        s -= nst;
         ph ^= 1u;
       }
-      PROF(p_issue += clock64() - t_a;)
+      PROF(p_issue += clock64() - t_a; ++p_n;)
     }
-    (void)alive;
-    PROF(if (pw == 7 && lane == 0 && blockIdx.x < 148) {
+    PROF(if (pw_all == 7 && lane == 0 && blockIdx.x < 148) {
       unsigned long long* o = g_conv_profile[blockIdx.x];
-      o[0] = clock64() - p_t0; o[1] = p_idx; o[2] = p_wait; o[3] = p_issue; o[4] = it;
+      o[0] = clock64() - p_t0; o[1] = p_idx; o[2] = p_wait; o[3] = p_issue; o[4] = 2 * p_n;
     })
     cp_async_wait_all();  // nothing of this thread may still be writing when the CTA exits
   } else if (warp == kMmaWarp) {

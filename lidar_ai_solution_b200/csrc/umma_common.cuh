@@ -36,15 +36,11 @@ struct UmmaArgs {
 };
 
 // Shared-memory footprint of one launch configuration (the kernel carves it the same way).
-__host__ __device__ inline size_t umma_idx_bytes(int rb) {
-  const int opc = rb <= kChunk ? kChunk / rb : 1;  // taps per chunk
-  return (size_t)8 * 4 * opc * 36 * sizeof(int32_t);  // 8 warps x 4 slots x taps x (32 rows + pad)
-}
-__host__ __device__ inline size_t umma_smem_bytes(int rb, int cout, int nchunk, int w_rep,
-                                                  int w_resident, int nstages) {
+__host__ __device__ inline size_t umma_smem_bytes(int cout, int nchunk, int w_rep, int w_resident,
+                                                  int nstages) {
   const size_t wchunk = (size_t)w_rep * cout * kChunk;
   const size_t w = w_resident ? (size_t)nchunk * wchunk : (size_t)nstages * wchunk;
-  return 1024 + w + (size_t)nstages * 256 * kChunk + umma_idx_bytes(rb) + 256;
+  return 1024 + w + (size_t)nstages * 256 * kChunk + 256;
 }
 
 // ------------------------------------------------------------- PTX wrappers
