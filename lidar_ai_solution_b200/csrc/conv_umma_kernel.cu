@@ -65,6 +65,13 @@
 #else
 #define PROF(...)
 #endif
+// The work switches alone (-DSPCONVB_CONV_SWITCHES, implied by the profile build): the same
+// experiments timed from outside, without the clock reads in the loops.
+#if defined(SPCONVB_CONV_PROFILE) || defined(SPCONVB_CONV_SWITCHES)
+#define DBG(...) __VA_ARGS__
+#else
+#define DBG(...)
+#endif
 
 namespace spconvb {
 
@@ -171,6 +178,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
 
   const int warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31;
+  PROF(const long long k_c0 = clock64(); const unsigned long long k_t0 = global_ns();)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kMaxStages; ++s) {
@@ -315,7 +323,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
     int32_t cur[8], nxt[8];
     load_idx(tile, j, cur);
     PROF(long long p_idx = 0, p_wait = 0, p_issue = 0, p_t0 = clock64(), t_a, t_b; uint32_t p_n = 0;)
-    PROF(const bool no_copies = a.wait_test < 0 && ((-a.wait_test) & 1);)
+    DBG(const bool no_copies = a.wait_test < 0 && ((-a.wait_test) & 1);)
     while (tile < ntiles) {
       PROF(t_a = clock64();)
       uint32_t ntile = tile;
@@ -337,7 +345,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
                      a.wpk + (size_t)j * (COUT * kChunk), COUT * kChunk, bar_full + 8 * s);
         }
       }
-      if (has_rows PROF(&& !no_copies)) {
+      if (has_rows DBG(&& !no_copies)) {
         const uint32_t byte = seg_byte + (RB > kChunk ? (uint32_t)(j % CPT) * kChunk : 0u);
         const uint32_t stage_addr = smem_u32(sR + s * kRowsBytes) + dst_base;
 #pragma unroll
@@ -381,69 +389,66 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
       uint32_t ph = 0, tl = 0;
       bool alive = true;
       if (w_resident && blockIdx.x < ntiles)
-        alive = mbar_wait(bar_w, 0u, abort_flag, a.status, 6u);
+        alive = mbar_wait_spin(bar_w, 0u, abort_flag, a.status, 6u);
       // The loop is entered with the current chunk's stage known to be full.
       if (blockIdx.x < ntiles && alive)
-        alive = mbar_wait(bar_full, 0u, abort_flag, a.status, 3u);
+        alive = mbar_wait_spin(bar_full, 0u, abort_flag, a.status, 3u);
       // The thread that issues the MMAs runs one lane of one warp: every instruction
       // between two MMAs that the tensor pipe cannot hide (it queues about one MMA ahead)
       // is a bubble.  So the loop carries its descriptors and barrier addresses along
       // instead of recomputing them, asks about the next stage once, early (right after
       // the first MMA, so the answer is there when the last one has been issued), and
       // issues the K steps of a full chunk without a loop.
+      // 32-bit arithmetic only: the descriptors differ in their low word (the address)
       const uint32_t w_step = w_chunk_smem >> 4, r_step = (uint32_t)(kRowsBytes >> 4);
-      uint64_t rd = rdesc0;                       // rows of the current stage
-      uint64_t wd_s = wdesc0;                     // weights of the current stage (streamed)
-      uint32_t full_s = bar_full, empty_s = bar_empty;
-      const uint32_t full_end = bar_full + 8 * nst;
+      const uint32_t desc_hi = (uint32_t)(wdesc0 >> 32);
+      const uint32_t w_lo0 = (uint32_t)wdesc0, r_lo0 = (uint32_t)rdesc0;
+      uint32_t s = 0;  // stage of the current chunk
       PROF(long long m_full = 0, m_issue = 0, m_tempty = 0, m_t0 = clock64(), t_a, t_b;)
-      PROF(const bool no_mma = a.wait_test < 0 && ((-a.wait_test) & 2);)
+      DBG(const bool no_mma = a.wait_test < 0 && ((-a.wait_test) & 2);)
       for (uint32_t tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x, ++tl) {
         const uint32_t buf = tl & 1u;
         PROF(t_a = clock64();)
-        if (!mbar_wait(bar_tempty + 8 * buf, ((tl >> 1) & 1u) ^ 1u, abort_flag, a.status, 2u))
+        if (!mbar_wait_spin(bar_tempty + 8 * buf, ((tl >> 1) & 1u) ^ 1u, abort_flag, a.status, 2u))
           break;
         PROF(m_tempty += clock64() - t_a;)
         tc_fence_after();  // the epilogue's reads of this accumulator come before these MMAs
         const uint32_t d_tmem = tmem_base + buf * kTileRows;
         const bool last_tile = tile + gridDim.x >= ntiles;
-        uint64_t wd_r = wdesc0;                   // weights of the current chunk (resident)
         for (int j = 0; j < nchunk; ++j) {
           // No fence here: the rows arrive by cp.async completions on the stage's mbarrier,
           // which is what the MMA's shared-memory reads are ordered behind.
-          const uint64_t wd = w_resident ? wd_r : wd_s;
+          const uint32_t rd = r_lo0 + s * r_step;
+          const uint32_t wd = w_lo0 + (w_resident ? (uint32_t)j : s) * w_step;
           // the next stage (of this tile's next chunk or of the next tile's first)
-          const bool wrap = full_s + 8 == full_end;
-          const uint32_t full_n = wrap ? bar_full : full_s + 8;
-          const uint32_t ph_n = wrap ? ph ^ 1u : ph;
+          const uint32_t s1 = s + 1 == nst ? 0u : s + 1;
+          const uint32_t ph1 = s1 == 0u ? ph ^ 1u : ph;
+          const uint32_t full_n = bar_full + 8 * s1;
           const bool more = j + 1 < nchunk || !last_tile;
           bool ready;
           PROF(t_a = clock64();)
-          PROF(if (no_mma) ready = !more || mbar_test_wait(full_n, ph_n); else)
+          DBG(if (no_mma) ready = !more || mbar_test_wait(full_n, ph1); else)
           if (j + 1 < nchunk) {
-            umma<INT8>(d_tmem, wd, rd, idesc, (uint32_t)(j != 0));
-            ready = mbar_test_wait(full_n, ph_n);
-            umma<INT8>(d_tmem, wd + 2u, rd + 2u, idesc, 1u);
-            umma<INT8>(d_tmem, wd + 4u, rd + 4u, idesc, 1u);
-            umma<INT8>(d_tmem, wd + 6u, rd + 6u, idesc, 1u);
+            umma_lohi<INT8>(d_tmem, wd, rd, desc_hi, idesc, (uint32_t)(j != 0));
+            ready = mbar_test_wait(full_n, ph1);
+            umma_lohi<INT8>(d_tmem, wd + 2u, rd + 2u, desc_hi, idesc, 1u);
+            umma_lohi<INT8>(d_tmem, wd + 4u, rd + 4u, desc_hi, idesc, 1u);
+            umma_lohi<INT8>(d_tmem, wd + 6u, rd + 6u, desc_hi, idesc, 1u);
           } else {
-            ready = !more || mbar_test_wait(full_n, ph_n);
+            ready = !more || mbar_test_wait(full_n, ph1);
             for (int ks = 0; ks < last_ksteps; ++ks)
-              umma<INT8>(d_tmem, wd + 2u * ks, rd + 2u * ks, idesc, (uint32_t)((j | ks) != 0));
+              umma_lohi<INT8>(d_tmem, wd + 2u * ks, rd + 2u * ks, desc_hi, idesc,
+                              (uint32_t)((j | ks) != 0));
           }
-          tc_commit(empty_s);
+          tc_commit(bar_empty + 8 * s);
           PROF(t_b = clock64(); m_issue += t_b - t_a;)
-          if (!ready && more && !mbar_wait(full_n, ph_n, abort_flag, a.status, 3u)) {
+          if (!ready && more && !mbar_wait_spin(full_n, ph1, abort_flag, a.status, 3u)) {
             alive = false;
             break;
           }
           PROF(m_full += clock64() - t_b;)
-          full_s = full_n;
-          ph = ph_n;
-          empty_s = wrap ? bar_empty : empty_s + 8;
-          rd = wrap ? rdesc0 : rd + r_step;
-          wd_s = wrap ? wdesc0 : wd_s + w_step;
-          wd_r += w_step;
+          s = s1;
+          ph = ph1;
         }
         if (alive) tc_commit(bar_tfull + 8 * buf);
       }
@@ -650,6 +655,10 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
   // ---------------------------------------------------------------- teardown
   tc_fence_before();
   __syncthreads();
+  PROF(if (threadIdx.x == 0 && blockIdx.x < 148) {
+    g_conv_profile[blockIdx.x][13] = clock64() - k_c0;   // SM cycles of the CTA ...
+    g_conv_profile[blockIdx.x][14] = global_ns() - k_t0;  // ... and the nanoseconds they took
+  })
   if (*abort_flag) {
     // give copies already issued a bounded time to land before the CTA exits
     const unsigned long long t0 = global_ns();

@@ -100,7 +100,13 @@ __device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t pari
       : "memory");
   return ok != 0;
 }
-// Bounded wait.  Returns false when the CTA is aborting.
+// Bounded waits.  They return false when the CTA is aborting.
+//
+// Two flavours.  A role whose wait is on the critical path of every chunk (the thread that
+// issues the MMAs) spins on the non-blocking test: a thread parked in try_wait wakes up late.
+// Roles that wait often and long (producers for a free stage, epilogue warps for a finished
+// tile) park in try_wait instead: a hot spin of 16 + 8 warps takes issue slots from the
+// warps that have work.  Both read the clock only after a first batch of polls has failed.
 static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity,
                                             volatile uint32_t* abort_flag, uint32_t* status,
                                             uint32_t where) {
@@ -116,15 +122,21 @@ static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity
     }
   }
 }
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
-                                          volatile uint32_t* abort_flag, uint32_t* status,
-                                          uint32_t where) {
-  // Most waits end within a microsecond or two: they spin on the non-blocking test (a
-  // thread parked in try_wait wakes up late).  The clock is only read, and the thread only
-  // parked, when that was not enough.
+__device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity,
+                                               volatile uint32_t* abort_flag, uint32_t* status,
+                                               uint32_t where) {
 #pragma unroll 1
   for (int i = 0; i < 256; ++i)
     if (mbar_test_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, abort_flag, status, where);
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
+                                          volatile uint32_t* abort_flag, uint32_t* status,
+                                          uint32_t where) {
+  if (mbar_test_wait(bar, parity)) return true;
+#pragma unroll 1
+  for (int i = 0; i < 64; ++i)
+    if (mbar_try_wait_parked(bar, parity, 2000u)) return true;
   return mbar_wait_slow(bar, parity, abort_flag, status, where);
 }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
@@ -194,6 +206,27 @@ __device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t adesc, uint64_t b
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+// The same with the shared-memory descriptors given as halves: only the low word (the
+// address field) changes from chunk to chunk, so the issuing thread does 32-bit arithmetic.
+template <bool INT8>
+__device__ __forceinline__ void umma_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo,
+                                          uint32_t desc_hi, uint32_t idesc, uint32_t accumulate) {
+  if (INT8) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %4, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
         : "memory");
   }
 }
