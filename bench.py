@@ -26,6 +26,9 @@ the ranks.
 Other measurements (not the headline):
     python bench.py --workload layer_sweep [--fp16]   # one SubM 3x3x3 layer, C x N sweep
     python bench.py --workload voxelizer              # the voxelizer alone
+    python bench.py --workload frame_once [--batch B] # one voxelizer call and one eager engine call
+                                                      # inside a cudaProfilerStart/Stop range (for
+                                                      # `ncu --profile-from-start off`)
 """
 from __future__ import annotations
 
@@ -827,6 +830,37 @@ def layer_case(torch, c, n, fp16, reps, flush, seed=0):
             "map_gbs": (16 * n + 4 * 27 * n) / us_map / 1e3}
 
 
+def run_frame_once(args):
+    """Everything a frame launches, exactly once, between cudaProfilerStart and cudaProfilerStop:
+    the voxelizer on a raw sweep, then one eager engine call on `--batch` synthetic frames."""
+    import torch
+    from lidar_ai_solution_b200 import cabi, engine, scenes
+    cabi.lib()
+    dev = torch.device("cuda", 0)
+    spec = WORKLOADS["centerpoint_int8"]
+    onnx_path = save_model(build_model(torch, spec))
+    B = max(1, args.batch)
+    frames = [workload_frame(spec, 1000 + i) for i in range(B)]
+    feats = np.concatenate([f for f, _ in frames])
+    coords = np.concatenate([np.concatenate([np.full((len(c), 1), b, np.int32), c[:, 1:]], 1)
+                             for b, (_, c) in enumerate(frames)])
+    df, dc = torch.from_numpy(feats).to(dev), torch.from_numpy(coords).to(dev)
+    e = engine.Engine.from_onnx(onnx_path, engine.PRECISION_INT8, 0, 0, dev)
+    e.forward(df, dc, GRID, batch=B)   # allocation and warm-up
+    pts = torch.from_numpy(scenes.make_points(140000, 7)).to(dev)
+    vox, bufs = make_voxelizer(torch, 140000, False)
+    vox(pts)
+    torch.cuda.synchronize()
+    torch.cuda.profiler.start()
+    vox(pts)
+    e.forward(df, dc, GRID, batch=B)
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    print(json.dumps({"workload": "frame_once", "frames": B, "launches": e.last_launches(),
+                      "status": e.status(), "voxels_from_points": int(bufs["n"].item())}))
+    e.close()
+
+
 def run_sweeps(args):
     import torch
     from lidar_ai_solution_b200 import cabi
@@ -848,7 +882,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="centerpoint_int8",
-                    choices=sorted(WORKLOADS) + ["layer_sweep", "voxelizer"])
+                    choices=sorted(WORKLOADS) + ["layer_sweep", "voxelizer", "frame_once"])
     ap.add_argument("--frames", type=int, default=16, help="frames per GPU per step")
     ap.add_argument("--batch", type=int, default=4, help="frames per engine call")
     ap.add_argument("--replicas", type=int, default=4, help="engine replicas (streams) per GPU")
@@ -872,6 +906,8 @@ def main():
         run_reference(args, rank, world)
     elif args.workload in ("layer_sweep", "voxelizer"):
         run_sweeps(args)
+    elif args.workload == "frame_once":
+        run_frame_once(args)
     else:
         run_gpu(args, rank, world, local_rank)
 

@@ -144,6 +144,22 @@ SPCONVB_API int spconvb_down_map(const int32_t* in_coords, const uint32_t* n_in_
                                  int32_t* map, uint64_t* out_table, uint32_t out_slots,
                                  uint32_t flags, uint32_t* status, void* stream);
 
+/* The same rulebook for input rows that were themselves produced by spconvb_down_map (or by
+ * this call): `in_workspace` is that call's workspace, still intact.  The map is then looked
+ * up from the output side by rank in the input's bitmap (one pass that writes every entry
+ * once) instead of being filled with -1 and scattered from the input side.  Results are
+ * identical to spconvb_down_map's. */
+SPCONVB_API int spconvb_down_map_ranked(const int32_t* in_coords, const uint32_t* n_in_ptr,
+                                        uint32_t cap_in, uint32_t launch_rows,
+                                        const int32_t in_grid[3], int32_t batch,
+                                        const int32_t ksize[3], const int32_t stride[3],
+                                        const int32_t pad[3], const int32_t dilation[3],
+                                        const void* in_workspace, void* workspace,
+                                        int32_t* out_coords, uint32_t* n_out_ptr,
+                                        uint32_t cap_out, int32_t* map, uint64_t* out_table,
+                                        uint32_t out_slots, uint32_t flags, uint32_t* status,
+                                        void* stream);
+
 /* Allocation-free variant of spconvb_down_map.  It has no counterpart in the
  * reference library; it exists for callers that are not allowed to allocate
  * device memory at all: a perception stack that freezes its memory map after

@@ -61,6 +61,9 @@ SYMBOLS = {
     "spconvb_down_map": (C.c_int, [_VP, _VP, C.c_uint32, C.c_uint32, _I3, C.c_int32, _I3, _I3, _I3,
                                    _I3, _VP, C.c_uint32, _VP, _VP, _VP, C.c_uint32, _VP, _VP,
                                    C.c_uint32, C.c_uint32, _VP, _VP]),
+    "spconvb_down_map_ranked": (C.c_int, [_VP, _VP, C.c_uint32, C.c_uint32, _I3, C.c_int32, _I3, _I3,
+                                          _I3, _I3, _VP, _VP, _VP, _VP, C.c_uint32, _VP, _VP,
+                                          C.c_uint32, C.c_uint32, _VP, _VP]),
     "spconvb_down_map_static": (C.c_int, [_VP, _VP, C.c_uint32, C.c_uint32, _I3, C.c_int32, _I3, _I3,
                                           _I3, _I3, _VP, C.c_uint32, _VP, _VP, C.c_uint32, _VP,
                                           _VP, C.c_uint32, C.c_uint32, _VP, _VP]),

@@ -894,11 +894,20 @@ int Engine::forward(const void* features, const int32_t* indices, uint32_t cap_r
         const Rule& R = rules[s.rule];
         const CoordSet& ci = coordsets[R.in_cs];
         CoordSet& co = coordsets[R.out_cs];
-        rc = spconvb_down_map(cs_coords(R.in_cs), cs_n(R.in_cs), cs_cap(R.in_cs),
-                              cs_launch(R.in_cs), ci.grid, batch, R.ksize, R.stride, R.pad, R.dil,
-                              ci.table, ci.slots, R.ws, co.coords, co.n_ptr, co.cap, R.map,
-                              co.table, co.slots, SPCONVB_FLAG_PREZEROED, status, st);
-        last_launches += 5 + (co.table ? 1 : 0);  // mark, scan, emit, map fill, scatter (+ hash)
+        if (ci.made_by_rule >= 0) {
+          // rows made by a strided rulebook: the map is looked up by rank from the output side
+          rc = spconvb_down_map_ranked(ci.coords, ci.n_ptr, ci.cap, ci.cap, ci.grid, batch, R.ksize,
+                                       R.stride, R.pad, R.dil, rules[ci.made_by_rule].ws, R.ws,
+                                       co.coords, co.n_ptr, co.cap, R.map, co.table, co.slots,
+                                       SPCONVB_FLAG_PREZEROED, status, st);
+          last_launches += 4 + (co.table ? 1 : 0);  // mark, scan, emit, gather (+ hash)
+        } else {
+          rc = spconvb_down_map(cs_coords(R.in_cs), cs_n(R.in_cs), cs_cap(R.in_cs),
+                                cs_launch(R.in_cs), ci.grid, batch, R.ksize, R.stride, R.pad,
+                                R.dil, ci.table, ci.slots, R.ws, co.coords, co.n_ptr, co.cap,
+                                R.map, co.table, co.slots, SPCONVB_FLAG_PREZEROED, status, st);
+          last_launches += 5 + (co.table ? 1 : 0);  // mark, scan, emit, map fill, scatter (+ hash)
+        }
         break;
       }
       case Step::INV_MAP: {

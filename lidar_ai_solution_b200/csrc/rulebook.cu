@@ -41,7 +41,17 @@ struct Kernel3 {
   int32_t s[3];
   int32_t p[3];
   int32_t d[3];
+  int32_t sh[3];  // log2 of the stride when it is a power of two (1, 2, 4, ...), else -1
 };
+
+// v % s == 0 and v / s for v >= 0, without the integer division when the stride is a power
+// of two (every strided layer of the lidar backbones has stride 1 or 2).
+__device__ __forceinline__ bool stride_divides(int v, int s, int sh) {
+  return sh >= 0 ? (v & (s - 1)) == 0 : v % s == 0;
+}
+__device__ __forceinline__ int stride_quotient(int v, int s, int sh) {
+  return sh >= 0 ? v >> sh : v / s;
+}
 
 // One thread per row: the row's coordinate is read once, its taps are walked in tap order
 // (so a warp's stores of one tap land in one or two lines of map[k][.]), and the lookups of
@@ -113,8 +123,11 @@ __device__ __forceinline__ bool tap_output_cell(const int4 c, int k, const Grid3
   const int v0 = c.y + kr.p[0] - k0 * kr.d[0];
   const int v1 = c.z + kr.p[1] - k1 * kr.d[1];
   const int v2 = c.w + kr.p[2] - k2 * kr.d[2];
-  if (v0 < 0 || v1 < 0 || v2 < 0 || v0 % kr.s[0] || v1 % kr.s[1] || v2 % kr.s[2]) return false;
-  const int o0 = v0 / kr.s[0], o1 = v1 / kr.s[1], o2 = v2 / kr.s[2];
+  if (v0 < 0 || v1 < 0 || v2 < 0 || !stride_divides(v0, kr.s[0], kr.sh[0]) ||
+      !stride_divides(v1, kr.s[1], kr.sh[1]) || !stride_divides(v2, kr.s[2], kr.sh[2]))
+    return false;
+  const int o0 = stride_quotient(v0, kr.s[0], kr.sh[0]), o1 = stride_quotient(v1, kr.s[1], kr.sh[1]),
+            o2 = stride_quotient(v2, kr.s[2], kr.sh[2]);
   if (o0 >= gout.g[0] || o1 >= gout.g[1] || o2 >= gout.g[2]) return false;
   *cell = voxel_key(c.x, o0, o1, o2, gout);
   return true;
@@ -129,18 +142,18 @@ __device__ __forceinline__ void for_each_output(const int4 c, const Grid3& gout,
                                                 F visit) {
   for (int k0 = 0; k0 < kr.k[0]; ++k0) {
     const int v0 = c.y + kr.p[0] - k0 * kr.d[0];
-    if (v0 < 0 || v0 % kr.s[0]) continue;
-    const int o0 = v0 / kr.s[0];
+    if (v0 < 0 || !stride_divides(v0, kr.s[0], kr.sh[0])) continue;
+    const int o0 = stride_quotient(v0, kr.s[0], kr.sh[0]);
     if (o0 >= gout.g[0]) continue;
     for (int k1 = 0; k1 < kr.k[1]; ++k1) {
       const int v1 = c.z + kr.p[1] - k1 * kr.d[1];
-      if (v1 < 0 || v1 % kr.s[1]) continue;
-      const int o1 = v1 / kr.s[1];
+      if (v1 < 0 || !stride_divides(v1, kr.s[1], kr.sh[1])) continue;
+      const int o1 = stride_quotient(v1, kr.s[1], kr.sh[1]);
       if (o1 >= gout.g[1]) continue;
       for (int k2 = 0; k2 < kr.k[2]; ++k2) {
         const int v2 = c.w + kr.p[2] - k2 * kr.d[2];
-        if (v2 < 0 || v2 % kr.s[2]) continue;
-        const int o2 = v2 / kr.s[2];
+        if (v2 < 0 || !stride_divides(v2, kr.s[2], kr.sh[2])) continue;
+        const int o2 = stride_quotient(v2, kr.s[2], kr.sh[2]);
         if (o2 >= gout.g[2]) continue;
         visit((k0 * kr.k[1] + k1) * kr.k[2] + k2, voxel_key(c.x, o0, o1, o2, gout));
       }
@@ -346,6 +359,48 @@ static bool is_k333(const Kernel3& kr) {
          kr.d[2] == 1;
 }
 
+static void set_stride_shifts(Kernel3& kr) {
+  for (int a = 0; a < 3; ++a) {
+    kr.sh[a] = -1;
+    for (int b = 0; b < 16; ++b)
+      if (kr.s[a] == (1 << b)) kr.sh[a] = b;
+  }
+}
+
+// Output-stationary form of the strided map, for inputs that were themselves made by a
+// strided rulebook (their bitmap and rank prefix exist): one thread per output row walks the
+// taps in tap order, finds the input cell of each (out * stride - pad + tap * dilation) and
+// ranks it in the input's bitmap.  Every map entry is written exactly once, so there is no
+// fill pass, and a warp's stores of one tap land in one or two lines of map[k][.].
+__global__ void down_gather_ranked_kernel(const int4* __restrict__ out_coords,
+                                          const uint32_t* n_out_ptr, uint32_t cap_out, Grid3 gin,
+                                          Kernel3 kr, DownWs in_ws, uint32_t cap_in,
+                                          int32_t* __restrict__ map) {
+  const uint32_t n = min(*n_out_ptr, cap_out);
+  for (uint32_t row = blockIdx.x * blockDim.x + threadIdx.x; row < n;
+       row += gridDim.x * blockDim.x) {
+    const int4 c = __ldg(out_coords + row);
+    int32_t* dst = map + row;
+    for (int k0 = 0; k0 < kr.k[0]; ++k0) {
+      const int p0 = c.y * kr.s[0] - kr.p[0] + k0 * kr.d[0];
+      const bool ok0 = (unsigned)p0 < (unsigned)gin.g[0];
+      for (int k1 = 0; k1 < kr.k[1]; ++k1) {
+        const int p1 = c.z * kr.s[1] - kr.p[1] + k1 * kr.d[1];
+        const bool ok1 = ok0 && (unsigned)p1 < (unsigned)gin.g[1];
+#pragma unroll 3
+        for (int k2 = 0; k2 < kr.k[2]; ++k2) {
+          const int p2 = c.w * kr.s[2] - kr.p[2] + k2 * kr.d[2];
+          int32_t r = -1;
+          if (ok1 && (unsigned)p2 < (unsigned)gin.g[2])
+            r = rank_lookup(in_ws.bitmap, in_ws.prefix, voxel_key(c.x, p0, p1, p2, gin), cap_in);
+          *dst = r;
+          dst += cap_out;
+        }
+      }
+    }
+  }
+}
+
 // Fixed-size grids: a multiple of the SM count, independent of the row count.
 static int flat_blocks(unsigned long long work_cap) {
   unsigned long long b = (work_cap + kThreads - 1) / kThreads;
@@ -536,6 +591,7 @@ int spconvb_inverse_map(const int32_t* coords, const uint32_t* n_ptr, uint32_t c
     og[a2] = spconvb_out_extent(grid[a2], ksize[a2], stride[a2], pad[a2], dilation[a2]);
     if (og[a2] < 1) return SPCONVB_E_ARG;
   }
+  set_stride_shifts(kr);
   const int kvol = ksize[0] * ksize[1] * ksize[2];
   if (kvol > 65535) return SPCONVB_E_ARG;
   if (!grid_fits(og, batch)) return SPCONVB_E_RANGE;
@@ -561,18 +617,17 @@ size_t spconvb_down_workspace_bytes(const int32_t out_grid[3], int32_t batch) {
   return sizeof(uint32_t) * (2 * words + blocks + 16);
 }
 
-int spconvb_down_map(const int32_t* in_coords, const uint32_t* n_in_ptr, uint32_t cap_in,
-                     uint32_t launch_rows, const int32_t in_grid[3], int32_t batch,
-                     const int32_t ksize[3], const int32_t stride[3], const int32_t pad[3],
-                     const int32_t dilation[3], const uint64_t* in_table, uint32_t in_slots,
-                     void* workspace, int32_t* out_coords, uint32_t* n_out_ptr, uint32_t cap_out,
-                     int32_t* map, uint64_t* out_table, uint32_t out_slots, uint32_t flags,
-                     uint32_t* status, void* stream) {
+// Shared body of spconvb_down_map and spconvb_down_map_ranked.
+static int down_map_impl(const int32_t* in_coords, const uint32_t* n_in_ptr, uint32_t cap_in,
+                         uint32_t launch_rows, const int32_t in_grid[3], int32_t batch,
+                         const int32_t ksize[3], const int32_t stride[3], const int32_t pad[3],
+                         const int32_t dilation[3], const void* in_workspace, void* workspace,
+                         int32_t* out_coords, uint32_t* n_out_ptr, uint32_t cap_out, int32_t* map,
+                         uint64_t* out_table, uint32_t out_slots, uint32_t flags,
+                         uint32_t* status, void* stream) {
   if (!in_coords || !n_in_ptr || !in_grid || !ksize || !stride || !pad || !dilation ||
       !workspace || !out_coords || !n_out_ptr || !map)
     return SPCONVB_E_ARG;
-  (void)in_table;
-  (void)in_slots;
   if (out_table && (out_slots < 2 || (out_slots & (out_slots - 1)) || out_slots < 2ull * cap_out))
     return SPCONVB_E_ARG;
   if (!grid_fits(in_grid, batch)) return SPCONVB_E_RANGE;
@@ -584,6 +639,7 @@ int spconvb_down_map(const int32_t* in_coords, const uint32_t* n_in_ptr, uint32_
     og[a] = spconvb_out_extent(in_grid[a], ksize[a], stride[a], pad[a], dilation[a]);
     if (og[a] < 1) return SPCONVB_E_ARG;
   }
+  set_stride_shifts(kr);
   if (!grid_fits(og, batch)) return SPCONVB_E_RANGE;
   const int kvol = ksize[0] * ksize[1] * ksize[2];
   if (kvol > 65535) return SPCONVB_E_ARG;
@@ -610,11 +666,24 @@ int spconvb_down_map(const int32_t* in_coords, const uint32_t* n_in_ptr, uint32_
   down_emit_kernel<<<ws.blocks, kScanThreads, 0, st>>>(ws, gout, (int4*)out_coords, n_out_ptr,
                                                        cap_out, status);
   SPCONVB_LAUNCH_CHECK();
-  map_fill_kernel<<<flat_blocks((unsigned long long)cap_out * kvol / 4 + 1), kThreads, 0, st>>>(
-      n_out_ptr, cap_out, kvol, map);
-  SPCONVB_LAUNCH_CHECK();
-  down_scatter_kernel<<<flat_blocks(launch_rows), kThreads, 0, st>>>(
-      (const int4*)in_coords, n_in_ptr, cap_in, gin, gout, kr, ws, cap_out, map);
+  if (in_workspace) {
+    // the inputs can be ranked: every map entry is looked up from the output side
+    DownWs in_ws;
+    in_ws.words = down_words(in_grid, batch);
+    in_ws.blocks = 0;
+    in_ws.bitmap = (uint32_t*)in_workspace;
+    in_ws.prefix = in_ws.bitmap + in_ws.words;
+    in_ws.block_sums = nullptr;
+    constexpr int kRowThreads = 128;
+    down_gather_ranked_kernel<<<row_blocks(cap_out, kRowThreads), kRowThreads, 0, st>>>(
+        (const int4*)out_coords, n_out_ptr, cap_out, gin, kr, in_ws, cap_in, map);
+  } else {
+    map_fill_kernel<<<flat_blocks((unsigned long long)cap_out * kvol / 4 + 1), kThreads, 0, st>>>(
+        n_out_ptr, cap_out, kvol, map);
+    SPCONVB_LAUNCH_CHECK();
+    down_scatter_kernel<<<flat_blocks(launch_rows), kThreads, 0, st>>>(
+        (const int4*)in_coords, n_in_ptr, cap_in, gin, gout, kr, ws, cap_out, map);
+  }
   if (out_table) {
     SPCONVB_LAUNCH_CHECK();
     hash_rows_kernel<<<flat_blocks(cap_out), kThreads, 0, st>>>(
@@ -622,6 +691,34 @@ int spconvb_down_map(const int32_t* in_coords, const uint32_t* n_in_ptr, uint32_
   }
   SPCONVB_LAUNCH_CHECK();
   return SPCONVB_OK;
+}
+
+int spconvb_down_map(const int32_t* in_coords, const uint32_t* n_in_ptr, uint32_t cap_in,
+                     uint32_t launch_rows, const int32_t in_grid[3], int32_t batch,
+                     const int32_t ksize[3], const int32_t stride[3], const int32_t pad[3],
+                     const int32_t dilation[3], const uint64_t* in_table, uint32_t in_slots,
+                     void* workspace, int32_t* out_coords, uint32_t* n_out_ptr, uint32_t cap_out,
+                     int32_t* map, uint64_t* out_table, uint32_t out_slots, uint32_t flags,
+                     uint32_t* status, void* stream) {
+  (void)in_table;
+  (void)in_slots;
+  return down_map_impl(in_coords, n_in_ptr, cap_in, launch_rows, in_grid, batch, ksize, stride,
+                       pad, dilation, nullptr, workspace, out_coords, n_out_ptr, cap_out, map,
+                       out_table, out_slots, flags, status, stream);
+}
+
+int spconvb_down_map_ranked(const int32_t* in_coords, const uint32_t* n_in_ptr, uint32_t cap_in,
+                            uint32_t launch_rows, const int32_t in_grid[3], int32_t batch,
+                            const int32_t ksize[3], const int32_t stride[3],
+                            const int32_t pad[3], const int32_t dilation[3],
+                            const void* in_workspace, void* workspace, int32_t* out_coords,
+                            uint32_t* n_out_ptr, uint32_t cap_out, int32_t* map,
+                            uint64_t* out_table, uint32_t out_slots, uint32_t flags,
+                            uint32_t* status, void* stream) {
+  if (!in_workspace) return SPCONVB_E_ARG;
+  return down_map_impl(in_coords, n_in_ptr, cap_in, launch_rows, in_grid, batch, ksize, stride,
+                       pad, dilation, in_workspace, workspace, out_coords, n_out_ptr, cap_out, map,
+                       out_table, out_slots, flags, status, stream);
 }
 
 int spconvb_down_map_static(const int32_t* in_coords, const uint32_t* n_in_ptr, uint32_t cap_in,

@@ -63,10 +63,12 @@ def out_grid(grid, ksize, stride, pad, dilation=(1, 1, 1)):
 
 
 def down_map(coords, n_ptr, grid, table, ksize, stride, pad, dilation=(1, 1, 1), cap_out=None,
-             batch=1, status=None, want_table=True, launch_rows=0, return_ws=False):
+             batch=1, status=None, want_table=True, launch_rows=0, return_ws=False, in_ws=None):
     """Returns (out_coords, n_out_ptr, map, out_table, out_grid) and, with ``return_ws``,
     the workspace (bitmap + rank prefix of the outputs) as a sixth item.  ``table`` is not
-    needed any more and may be None."""
+    needed any more and may be None.  ``in_ws``: the workspace of the down_map call that made
+    ``coords``; the map is then looked up by rank from the output side
+    (spconvb_down_map_ranked), with the same result."""
     dev = coords.device
     cap_in = coords.shape[0]
     og = out_grid(grid, ksize, stride, pad, dilation)
@@ -80,12 +82,19 @@ def down_map(coords, n_ptr, grid, table, ksize, stride, pad, dilation=(1, 1, 1),
     m = torch.full((kvol, cap_out), -1, dtype=torch.int32, device=dev)
     slots = cabi.lib().spconvb_hash_slots(cap_out) if want_table else 0
     otab = torch.empty(slots, dtype=torch.int64, device=dev) if want_table else None
-    cabi.check(cabi.lib().spconvb_down_map(
-        _ptr(coords), _ptr(n_ptr), cap_in, launch_rows, cabi.i3(grid), batch, cabi.i3(ksize),
-        cabi.i3(stride), cabi.i3(pad), cabi.i3(dilation), _ptr(table),
-        table.numel() if table is not None else 0, _ptr(ws),
-        _ptr(oc), _ptr(n_out), cap_out, _ptr(m), _ptr(otab), slots, 0, _ptr(status), _stream()),
-        "down_map")
+    if in_ws is not None:
+        cabi.check(cabi.lib().spconvb_down_map_ranked(
+            _ptr(coords), _ptr(n_ptr), cap_in, launch_rows, cabi.i3(grid), batch, cabi.i3(ksize),
+            cabi.i3(stride), cabi.i3(pad), cabi.i3(dilation), _ptr(in_ws), _ptr(ws),
+            _ptr(oc), _ptr(n_out), cap_out, _ptr(m), _ptr(otab), slots, 0, _ptr(status),
+            _stream()), "down_map_ranked")
+    else:
+        cabi.check(cabi.lib().spconvb_down_map(
+            _ptr(coords), _ptr(n_ptr), cap_in, launch_rows, cabi.i3(grid), batch, cabi.i3(ksize),
+            cabi.i3(stride), cabi.i3(pad), cabi.i3(dilation), _ptr(table),
+            table.numel() if table is not None else 0, _ptr(ws),
+            _ptr(oc), _ptr(n_out), cap_out, _ptr(m), _ptr(otab), slots, 0, _ptr(status),
+            _stream()), "down_map")
     if return_ws:
         return oc, n_out, m, otab, og, ws
     return oc, n_out, m, otab, og

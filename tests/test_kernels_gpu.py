@@ -100,8 +100,17 @@ def _chain(coords, grid):
             m = ops.subm_map_ranked(dc, n_ptr, grid, ws, status=st)
             by_hash = ops.subm_map(dc, n_ptr, grid, table, status=st)
             assert torch.equal(m[:, : int(n_ptr.item())], by_hash[:, : int(n_ptr.item())])
+        in_ws = ws
         oc, n_out, dm, otab, og, ws = ops.down_map(dc, n_ptr, grid, None, k, s, p, status=st,
                                                    return_ws=True)
+        if in_ws is not None:
+            # rows made by a strided rulebook: the output-side lookup by rank gives the same
+            # coordinates, count and map as the input-side scatter
+            oc2, n2, dm2, _, _ = ops.down_map(dc, n_ptr, grid, None, k, s, p, status=st,
+                                              in_ws=in_ws)
+            kk = int(n_out.item())
+            assert int(n2.item()) == kk and torch.equal(oc2[:kk], oc[:kk])
+            assert torch.equal(dm2[:, :kk], dm[:, :kk])
         torch.cuda.synchronize()
         _status_ok(st)
         out.append((dc, n_ptr, list(grid), m, oc, n_out, dm, og))
