@@ -219,9 +219,8 @@ __global__ void __launch_bounds__(kScanThreads) down_scan_kernel(DownWs ws) {
   if (w < ws.words) ws.prefix[w] = warp_sums[warp] + incl - local;
 }
 
-// Ranks every set bit (one word per thread, so at most 32 rows each): writes
-// the output coordinate, makes the prefix global, and the last block publishes the
-// count.  No atomics.
+// Ranks every set bit: writes the output coordinate, makes the prefix global, and the
+// last block publishes the count.  No atomics.
 __global__ void __launch_bounds__(kScanThreads)
 down_emit_kernel(DownWs ws, Grid3 gout, int4* __restrict__ out_coords, uint32_t* n_out_ptr,
                  uint32_t cap_out, uint32_t* status) {
@@ -247,33 +246,47 @@ down_emit_kernel(DownWs ws, Grid3 gout, int4* __restrict__ out_coords, uint32_t*
     }
   }
   __syncthreads();
+  // Every thread reads one word and makes its prefix global; then the warp goes through its
+  // non-empty words together, one lane per bit: the rows of a word are consecutive, so the
+  // coordinate stores of a word coalesce, and no lane loops over the bits of a dense word
+  // while the others wait.
   const uint32_t w = blockIdx.x * kScanWordsPerBlock + threadIdx.x;
-  if (w >= ws.words) return;
-  uint32_t bits = ws.bitmap[w];
-  uint32_t row = s_base + ws.prefix[w];
-  ws.prefix[w] = row;
-  if (!bits) return;
-  // decode the word's first cell once, then walk the set bits
-  uint32_t t = w << 5;
-  int c2 = t % gout.g[2]; t /= gout.g[2];
-  int c1 = t % gout.g[1]; t /= gout.g[1];
-  int c0 = t % gout.g[0]; t /= gout.g[0];
-  int bq = (int)t;
-  int prev = 0;
-  while (bits) {
-    const int b = __ffs(bits) - 1;
-    bits &= bits - 1;
-    c2 += b - prev;
-    prev = b;
-    while (c2 >= gout.g[2]) {
-      c2 -= gout.g[2];
-      if (++c1 >= gout.g[1]) {
-        c1 = 0;
-        if (++c0 >= gout.g[0]) { c0 = 0; ++bq; }
-      }
+  const uint32_t lane = threadIdx.x & 31u;
+  uint32_t bits = 0, row0 = 0;
+  int c2 = 0, c1 = 0, c0 = 0, bq = 0;
+  if (w < ws.words) {
+    bits = ws.bitmap[w];
+    row0 = s_base + ws.prefix[w];
+    ws.prefix[w] = row0;
+    if (bits) {  // the word's first cell
+      uint32_t t = w << 5;
+      c2 = t % gout.g[2]; t /= gout.g[2];
+      c1 = t % gout.g[1]; t /= gout.g[1];
+      c0 = t % gout.g[0]; t /= gout.g[0];
+      bq = (int)t;
     }
-    if (row < cap_out) out_coords[row] = make_int4(bq, c0, c1, c2);
-    ++row;
+  }
+  uint32_t nonempty = __ballot_sync(0xffffffffu, bits != 0u);
+  while (nonempty) {
+    const int src = __ffs(nonempty) - 1;
+    nonempty &= nonempty - 1;
+    const uint32_t wb = __shfl_sync(0xffffffffu, bits, src);
+    const uint32_t r0 = __shfl_sync(0xffffffffu, row0, src);
+    int x = __shfl_sync(0xffffffffu, c2, src) + (int)lane;
+    int y = __shfl_sync(0xffffffffu, c1, src);
+    int z = __shfl_sync(0xffffffffu, c0, src);
+    int b = __shfl_sync(0xffffffffu, bq, src);
+    if ((wb >> lane) & 1u) {
+      const uint32_t row = r0 + __popc(wb & ((1u << lane) - 1u));
+      while (x >= gout.g[2]) {
+        x -= gout.g[2];
+        if (++y >= gout.g[1]) {
+          y = 0;
+          if (++z >= gout.g[0]) { z = 0; ++b; }
+        }
+      }
+      if (row < cap_out) out_coords[row] = make_int4(b, z, y, x);
+    }
   }
 }
 
