@@ -233,11 +233,11 @@ def step_work(line, rows_of, pairs_of, dense_elems):
 
 
 # DRAM bytes (read + write) per algorithmic byte of a convolution launch, by the row width
-# of its input in bytes: ratios of one ncu capture per width (dram__bytes_read.sum +
-# dram__bytes_write.sum over the launch's algorithmic bytes; the output is still in L2 when
-# the launch ends, so the ratio is below 1).  ncu cannot capture a whole frame within its
-# size limits, so a frame's traffic is these ratios weighted by each layer's bytes.
-CONV_DRAM_RATIO = {16: 0.89, 32: 0.81, 64: 0.73, 128: 0.70, 256: 0.70}
+# of its input in bytes: from one ncu counter pass over every launch of a batch of 4 frames
+# of this workload (`--workload frame_once --batch 4`; dram__bytes_read.sum +
+# dram__bytes_write.sum of the launches of a width over their algorithmic bytes; 0.92 over
+# all 21).  A frame's traffic is these ratios weighted by each layer's bytes.
+CONV_DRAM_RATIO = {16: 0.91, 32: 0.93, 64: 0.96, 128: 0.79, 256: 0.79}
 
 
 # ------------------------------------------------------------ reference arm
@@ -563,10 +563,11 @@ def make_voxelizer(torch, n_points, fp16, max_voxels=160000):
 
 
 def time_launches(torch, fn, reps, flush):
-    """Mean microseconds of fn() over `reps` runs, an L2 flush (a 256 MB write) before each."""
+    """Median microseconds of fn() over `reps` runs, an L2 flush (a 256 MB write) before each
+    (the median, because a helper that allocates its result can stall one run on the host)."""
     start = torch.cuda.Event(enable_timing=True)
     end = torch.cuda.Event(enable_timing=True)
-    total = 0.0
+    times = []
     for i in range(reps):
         if flush is not None:
             flush.fill_(i & 0xFF)
@@ -574,8 +575,8 @@ def time_launches(torch, fn, reps, flush):
         fn()
         end.record()
         end.synchronize()
-        total += start.elapsed_time(end)
-    return total / reps * 1000.0
+        times.append(start.elapsed_time(end))
+    return float(np.median(times)) * 1000.0
 
 
 def from_points_leg(torch, dev, onnx_path, precision, steps):
@@ -814,10 +815,10 @@ def layer_case(torch, c, n, fp16, reps, flush, seed=0):
     if int(st.cpu()[0]):
         raise RuntimeError("device status %s" % st.cpu().tolist())
     us = time_launches(torch, conv, reps, flush)
-    us_hash = time_launches(torch, lambda: ops.hash_build(coords, n_ptr, GRID), max(1, reps // 4),
+    us_hash = time_launches(torch, lambda: ops.hash_build(coords, n_ptr, GRID), max(3, reps // 4),
                             flush)
     us_map = time_launches(torch, lambda: ops.subm_map(coords, n_ptr, GRID, table),
-                           max(1, reps // 4), flush)
+                           max(3, reps // 4), flush)
     pairs = int((m >= 0).sum().item())
     nbytes = n * c * es * 2 + 27 * c * c * es + c * 8 + 4 * 27 * n
     opsn = 2 * pairs * c * c
@@ -883,8 +884,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="centerpoint_int8",
                     choices=sorted(WORKLOADS) + ["layer_sweep", "voxelizer", "frame_once"])
-    ap.add_argument("--frames", type=int, default=16, help="frames per GPU per step")
-    ap.add_argument("--batch", type=int, default=4, help="frames per engine call")
+    ap.add_argument("--frames", type=int, default=32, help="frames per GPU per step")
+    ap.add_argument("--batch", type=int, default=8, help="frames per engine call")
     ap.add_argument("--replicas", type=int, default=4, help="engine replicas (streams) per GPU")
     ap.add_argument("--legs", default="config4,real_frame,voxelizer,copy_only",
                     help="extra measurements added to the line (comma separated; '' for none)")
