@@ -345,7 +345,10 @@ __global__ void __launch_bounds__(kCtaThreads, 1) conv_umma_kernel(const UmmaArg
                      a.wpk + (size_t)j * (COUT * kChunk), COUT * kChunk, bar_full + 8 * s);
         }
       }
-      if (has_rows DBG(&& !no_copies)) {
+      // segments of the last chunk that lie in K steps past the kernel's last tap are never
+      // read by an MMA: nothing to copy, nothing to zero
+      const bool dead_seg = j == nchunk - 1 && (int)(seg >> 1) >= last_ksteps;
+      if (has_rows && !dead_seg DBG(&& !no_copies)) {
         const uint32_t byte = seg_byte + (RB > kChunk ? (uint32_t)(j % CPT) * kChunk : 0u);
         const uint32_t stage_addr = smem_u32(sR + s * kRowsBytes) + dst_base;
 #pragma unroll
