@@ -161,16 +161,53 @@ __device__ __forceinline__ void for_each_output(const int4 c, const Grid3& gout,
   }
 }
 
+// With dilation 1 the outputs an input coordinate c reaches along one axis are a range:
+// tap k = c + pad - o * stride lies in [0, K) exactly for
+// ceil((c + pad - K + 1) / stride) <= o <= floor((c + pad) / stride), clipped to the grid.
+// No divisibility tests, no tap loop.
+struct AxisRange { int lo, hi; };
+__device__ __forceinline__ AxisRange output_range(int c, int a, const Grid3& gout,
+                                                  const Kernel3& kr) {
+  const int top = c + kr.p[a], t = top - kr.k[a] + 1;
+  AxisRange r;
+  r.hi = min(stride_quotient(top, kr.s[a], kr.sh[a]), gout.g[a] - 1);
+  r.lo = t <= 0 ? 0 : stride_quotient(t + kr.s[a] - 1, kr.s[a], kr.sh[a]);
+  return r;
+}
+__host__ __device__ inline bool unit_dilation(const Kernel3& kr) {
+  return kr.d[0] == 1 && kr.d[1] == 1 && kr.d[2] == 1;
+}
+
 __global__ void down_mark_kernel(const int4* __restrict__ coords, const uint32_t* n_ptr,
                                  uint32_t cap, Grid3 gin, Grid3 gout, Kernel3 kr,
                                  uint32_t* bitmap) {
   const uint32_t n = min(*n_ptr, cap);
+  const bool unit = unit_dilation(kr) && kr.k[2] <= 32 * kr.s[2];
   for (uint32_t row = blockIdx.x * blockDim.x + threadIdx.x; row < n;
        row += gridDim.x * blockDim.x) {
     const int4 c = __ldg(coords + row);
     if ((unsigned)c.x >= (unsigned)gin.batch) continue;
+    if (unit) {
+      // the reached cells are a box; its cells along the innermost axis are adjacent bits,
+      // set with one atomic (two when the run crosses a word)
+      const AxisRange r0 = output_range(c.y, 0, gout, kr), r1 = output_range(c.z, 1, gout, kr),
+                      r2 = output_range(c.w, 2, gout, kr);
+      if (r2.lo > r2.hi) continue;
+      const uint32_t nbits = (uint32_t)(r2.hi - r2.lo + 1);
+      for (int o0 = r0.lo; o0 <= r0.hi; ++o0)
+        for (int o1 = r1.lo; o1 <= r1.hi; ++o1) {
+          const uint32_t cell = voxel_key(c.x, o0, o1, r2.lo, gout);
+          const unsigned long long run =
+              (nbits >= 64u ? ~0ull : (1ull << nbits) - 1ull) << (cell & 31u);
+          uint32_t* word = bitmap + (cell >> 5);
+          const uint32_t m0 = (uint32_t)run, m1 = (uint32_t)(run >> 32);
+          // up to kvol inputs reach the same cells: look before the atomic, most find them set
+          if ((*(volatile uint32_t*)word & m0) != m0) atomicOr(word, m0);
+          if (m1 && (*(volatile uint32_t*)(word + 1) & m1) != m1) atomicOr(word + 1, m1);
+        }
+      continue;
+    }
     for_each_output(c, gout, kr, [&](int, uint32_t cell) {
-      // up to kvol inputs reach the same cell: look before the atomic, most find the bit set
       const uint32_t bit = 1u << (cell & 31);
       uint32_t* word = bitmap + (cell >> 5);
       if (!(*(volatile uint32_t*)word & bit)) atomicOr(word, bit);
@@ -318,10 +355,28 @@ __global__ void down_scatter_kernel(const int4* __restrict__ coords, const uint3
                                     uint32_t cap, Grid3 gin, Grid3 gout, Kernel3 kr, DownWs ws,
                                     uint32_t cap_out, int32_t* __restrict__ map) {
   const uint32_t n = min(*n_ptr, cap);
+  const bool unit = unit_dilation(kr);
   for (uint32_t row = blockIdx.x * blockDim.x + threadIdx.x; row < n;
        row += gridDim.x * blockDim.x) {
     const int4 c = __ldg(coords + row);
     if ((unsigned)c.x >= (unsigned)gin.batch) continue;
+    if (unit) {
+      const AxisRange r0 = output_range(c.y, 0, gout, kr), r1 = output_range(c.z, 1, gout, kr),
+                      r2 = output_range(c.w, 2, gout, kr);
+      for (int o0 = r0.lo; o0 <= r0.hi; ++o0) {
+        const int k0 = c.y + kr.p[0] - o0 * kr.s[0];
+        for (int o1 = r1.lo; o1 <= r1.hi; ++o1) {
+          const int k01 = k0 * kr.k[1] + (c.z + kr.p[1] - o1 * kr.s[1]);
+          for (int o2 = r2.lo; o2 <= r2.hi; ++o2) {
+            const int k = k01 * kr.k[2] + (c.w + kr.p[2] - o2 * kr.s[2]);
+            const int32_t o =
+                rank_lookup(ws.bitmap, ws.prefix, voxel_key(c.x, o0, o1, o2, gout), cap_out);
+            if (o >= 0) map[(size_t)k * cap_out + o] = (int32_t)row;
+          }
+        }
+      }
+      continue;
+    }
     for_each_output(c, gout, kr, [&](int k, uint32_t cell) {
       const int32_t o = rank_lookup(ws.bitmap, ws.prefix, cell, cap_out);
       if (o >= 0) map[(size_t)k * cap_out + o] = (int32_t)row;
