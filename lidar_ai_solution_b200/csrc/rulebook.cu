@@ -440,6 +440,7 @@ static void set_stride_shifts(Kernel3& kr) {
 // taps in tap order, finds the input cell of each (out * stride - pad + tap * dilation) and
 // ranks it in the input's bitmap.  Every map entry is written exactly once, so there is no
 // fill pass, and a warp's stores of one tap land in one or two lines of map[k][.].
+template <bool K333>
 __global__ void down_gather_ranked_kernel(const int4* __restrict__ out_coords,
                                           const uint32_t* n_out_ptr, uint32_t cap_out, Grid3 gin,
                                           Kernel3 kr, DownWs in_ws, uint32_t cap_in,
@@ -449,6 +450,30 @@ __global__ void down_gather_ranked_kernel(const int4* __restrict__ out_coords,
        row += gridDim.x * blockDim.x) {
     const int4 c = __ldg(out_coords + row);
     int32_t* dst = map + row;
+    if (K333) {
+      // 3x3x3, dilation 1: the taps unrolled, 27 independent rank lookups
+      const bool bok = (unsigned)c.x < (unsigned)gin.batch;
+#pragma unroll
+      for (int k0 = 0; k0 < 3; ++k0) {
+        const int p0 = c.y * kr.s[0] - kr.p[0] + k0;
+        const bool ok0 = bok && (unsigned)p0 < (unsigned)gin.g[0];
+#pragma unroll
+        for (int k1 = 0; k1 < 3; ++k1) {
+          const int p1 = c.z * kr.s[1] - kr.p[1] + k1;
+          const bool ok1 = ok0 && (unsigned)p1 < (unsigned)gin.g[1];
+#pragma unroll
+          for (int k2 = 0; k2 < 3; ++k2) {
+            const int p2 = c.w * kr.s[2] - kr.p[2] + k2;
+            int32_t r = -1;
+            if (ok1 && (unsigned)p2 < (unsigned)gin.g[2])
+              r = rank_lookup(in_ws.bitmap, in_ws.prefix, voxel_key(c.x, p0, p1, p2, gin), cap_in);
+            *dst = r;
+            dst += cap_out;
+          }
+        }
+      }
+      continue;
+    }
     for (int k0 = 0; k0 < kr.k[0]; ++k0) {
       const int p0 = c.y * kr.s[0] - kr.p[0] + k0 * kr.d[0];
       const bool ok0 = (unsigned)p0 < (unsigned)gin.g[0];
@@ -743,8 +768,12 @@ static int down_map_impl(const int32_t* in_coords, const uint32_t* n_in_ptr, uin
     in_ws.prefix = in_ws.bitmap + in_ws.words;
     in_ws.block_sums = nullptr;
     constexpr int kRowThreads = 128;
-    down_gather_ranked_kernel<<<row_blocks(cap_out, kRowThreads), kRowThreads, 0, st>>>(
-        (const int4*)out_coords, n_out_ptr, cap_out, gin, kr, in_ws, cap_in, map);
+    if (is_k333(kr))
+      down_gather_ranked_kernel<true><<<row_blocks(cap_out, kRowThreads), kRowThreads, 0, st>>>(
+          (const int4*)out_coords, n_out_ptr, cap_out, gin, kr, in_ws, cap_in, map);
+    else
+      down_gather_ranked_kernel<false><<<row_blocks(cap_out, kRowThreads), kRowThreads, 0, st>>>(
+          (const int4*)out_coords, n_out_ptr, cap_out, gin, kr, in_ws, cap_in, map);
   } else {
     map_fill_kernel<<<flat_blocks((unsigned long long)cap_out * kvol / 4 + 1), kThreads, 0, st>>>(
         n_out_ptr, cap_out, kvol, map);
