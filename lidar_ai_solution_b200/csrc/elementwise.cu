@@ -269,6 +269,17 @@ __global__ void scatter_dense_layout_kernel(const void* __restrict__ feat, int i
 
 static inline uint32_t clamp_u32(size_t v) { return v > 0xffffffffull ? 0xffffffffu : (uint32_t)v; }
 
+// the two dense launchers with the zero fill optional (declared for the engine in engine.hpp)
+int scatter_dense_launch(const void* feat, int32_t in_kind, float in_scale, const int32_t* coords,
+                         const uint32_t* n_ptr, uint32_t launch_rows, int32_t channels,
+                         int32_t batch, const int32_t grid[3], const int32_t perm[3], void* out,
+                         bool clear, void* stream);
+int scatter_dense_layout_launch(const void* feat, int32_t in_kind, float in_scale,
+                                const int32_t* coords, const uint32_t* n_ptr, uint32_t launch_rows,
+                                int32_t channels, int32_t batch, const int32_t grid[3],
+                                const int32_t perm[3], int32_t layout, int32_t out_kind,
+                                float inv_out_scale, void* out, bool clear, void* stream);
+
 }  // namespace spconvb
 
 using namespace spconvb;
@@ -347,6 +358,15 @@ int spconvb_scatter_dense(const void* feat, int32_t in_kind, float in_scale,
                           const int32_t* coords, const uint32_t* n_ptr, uint32_t launch_rows,
                           int32_t channels, int32_t batch, const int32_t grid[3],
                           const int32_t perm[3], void* out, void* stream) {
+  return spconvb::scatter_dense_launch(feat, in_kind, in_scale, coords, n_ptr, launch_rows,
+                                       channels, batch, grid, perm, out, true, stream);
+}
+
+extern "C++" int spconvb::scatter_dense_launch(const void* feat, int32_t in_kind, float in_scale,
+                                  const int32_t* coords, const uint32_t* n_ptr,
+                                  uint32_t launch_rows, int32_t channels, int32_t batch,
+                                  const int32_t grid[3], const int32_t perm[3], void* out,
+                                  bool clear, void* stream) {
   if (!feat || !coords || !n_ptr || !grid || !out || channels < 1 || channels > 1024 ||
       batch < 1 || launch_rows < 1)
     return SPCONVB_E_ARG;
@@ -374,7 +394,7 @@ int spconvb_scatter_dense(const void* feat, int32_t in_kind, float in_scale,
   g.g[0] = grid[0]; g.g[1] = grid[1]; g.g[2] = grid[2];
   g.batch = batch;
   const size_t bytes = sizeof(__half) * (size_t)batch * channels * grid[0] * grid[1] * grid[2];
-  SPCONVB_CUDA_TRY(cudaMemsetAsync(out, 0, bytes, st));
+  if (clear) SPCONVB_CUDA_TRY(cudaMemsetAsync(out, 0, bytes, st));
   size_t want_blocks = ((size_t)launch_rows + 31) / 32;
   if (want_blocks > (size_t)kSmCount * 16) want_blocks = (size_t)kSmCount * 16;
   const int blocks = (int)want_blocks;
@@ -390,10 +410,21 @@ int spconvb_scatter_dense_layout(const void* feat, int32_t in_kind, float in_sca
                                  uint32_t launch_rows, int32_t channels, int32_t batch,
                                  const int32_t grid[3], const int32_t perm[3], int32_t layout,
                                  int32_t out_kind, float inv_out_scale, void* out, void* stream) {
+  return spconvb::scatter_dense_layout_launch(feat, in_kind, in_scale, coords, n_ptr, launch_rows,
+                                              channels, batch, grid, perm, layout, out_kind,
+                                              inv_out_scale, out, true, stream);
+}
+
+extern "C++" int spconvb::scatter_dense_layout_launch(const void* feat, int32_t in_kind, float in_scale,
+                                         const int32_t* coords, const uint32_t* n_ptr,
+                                         uint32_t launch_rows, int32_t channels, int32_t batch,
+                                         const int32_t grid[3], const int32_t perm[3],
+                                         int32_t layout, int32_t out_kind, float inv_out_scale,
+                                         void* out, bool clear, void* stream) {
   if (layout == 0) layout = 1;
   if (layout == 1 && out_kind == SPCONVB_F16)
-    return spconvb_scatter_dense(feat, in_kind, in_scale, coords, n_ptr, launch_rows, channels,
-                                 batch, grid, perm, out, stream);
+    return scatter_dense_launch(feat, in_kind, in_scale, coords, n_ptr, launch_rows, channels,
+                                batch, grid, perm, out, clear, stream);
   if (!feat || !coords || !n_ptr || !grid || !out || channels < 1 || channels > 1024 ||
       batch < 1 || launch_rows < 1 || layout < 1 || layout > 3 ||
       (out_kind != SPCONVB_F16 && out_kind != SPCONVB_I8) ||
@@ -410,7 +441,7 @@ int spconvb_scatter_dense_layout(const void* feat, int32_t in_kind, float in_sca
   g.g[0] = grid[0]; g.g[1] = grid[1]; g.g[2] = grid[2];
   g.batch = batch;
   const size_t bytes = spconvb_dense_bytes(channels, batch, grid, perm, layout, out_kind);
-  SPCONVB_CUDA_TRY(cudaMemsetAsync(out, 0, bytes, st));
+  if (clear) SPCONVB_CUDA_TRY(cudaMemsetAsync(out, 0, bytes, st));
   // int8 rows stored with the scale the dense tensor is asked in are copied byte for byte
   const int copy_bytes = in_kind == SPCONVB_I8 && out_kind == SPCONVB_I8 &&
                          fabsf(in_scale * inv_out_scale - 1.f) < 1e-6f;

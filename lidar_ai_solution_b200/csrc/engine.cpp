@@ -866,6 +866,7 @@ int Engine::forward(const void* features, const int32_t* indices, uint32_t cap_r
     return cs_cap(c);
   };
 
+  bool clear_dense = true;  // false while a dense step's output was zeroed ahead of time
   auto run_step = [&](const Step& s) -> int {
     int rc = SPCONVB_OK;
     switch (s.kind) {
@@ -951,10 +952,11 @@ int Engine::forward(const void* features, const int32_t* indices, uint32_t cap_r
         break;
       case Step::DENSE: {
         const CoordSet& cs = coordsets[s.cs];
-        rc = spconvb_scatter_dense_layout(rt[s.in0].data, rt[s.in0].kind, s.a_scale,
-                                          cs_coords(s.cs), cs_n(s.cs), cs_launch(s.cs), s.cout,
-                                          batch, cs.grid, s.has_perm ? s.perm : nullptr, s.layout,
-                                          rt[s.out].kind, s.inv_out, rt[s.out].data, st);
+        rc = scatter_dense_layout_launch(rt[s.in0].data, rt[s.in0].kind, s.a_scale,
+                                         cs_coords(s.cs), cs_n(s.cs), cs_launch(s.cs), s.cout,
+                                         batch, cs.grid, s.has_perm ? s.perm : nullptr, s.layout,
+                                         rt[s.out].kind, s.inv_out, rt[s.out].data, clear_dense,
+                                         st);
         last_launches += 2;  // the zero fill and the scatter
         break;
       }
@@ -979,8 +981,27 @@ int Engine::forward(const void* features, const int32_t* indices, uint32_t cap_r
         cudaStreamWaitEvent(aux_, fork_ev_, 0) != cudaSuccess)
       return SPCONVB_E_DEVICE;
   }
-  for (size_t si = 0; si < steps.size(); ++si) {
+  // Dense outputs are zeroed on the auxiliary stream right away (bandwidth the convolutions
+  // leave unused) when a rulebook step precedes the dense step: its event, which the dense step
+  // waits for, then also covers the zero fill.
+  std::vector<char> precleared(steps.size(), 0);
+  if (fork) {
+    bool rule_seen = false;
+    for (size_t si = 0; si < steps.size() && rc == SPCONVB_OK; ++si) {
+      const Step& s = steps[si];
+      if (is_rulebook_step(s)) rule_seen = true;
+      if (s.kind != Step::DENSE || !rule_seen) continue;
+      const CoordSet& cs = coordsets[s.cs];
+      const size_t bytes = spconvb_dense_bytes(s.cout, batch, cs.grid, s.has_perm ? s.perm : nullptr,
+                                               s.layout, rt[s.out].kind);
+      if (bytes == 0) continue;
+      if (cudaMemsetAsync(rt[s.out].data, 0, bytes, aux_) != cudaSuccess) rc = SPCONVB_E_DEVICE;
+      else precleared[si] = 1;
+    }
+  }
+  for (size_t si = 0; si < steps.size() && rc == SPCONVB_OK; ++si) {
     const Step& s = steps[si];
+    clear_dense = !precleared[si];
     if (fork) {
       if (is_rulebook_step(s)) {
         st = aux_;

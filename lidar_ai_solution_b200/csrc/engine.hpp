@@ -20,6 +20,17 @@ enum { LOG_VERB = 0, LOG_WARN = 1, LOG_ERROR = 2 };
 int launch_set_count(uint32_t* dst, uint32_t value, cudaStream_t st);
 int launch_clamp_count(uint32_t* dst, const uint32_t* src, uint32_t cap, uint32_t* status,
                        cudaStream_t st);
+// spconvb_scatter_dense / spconvb_scatter_dense_layout with the zero fill of `out` optional
+// (clear = false: the caller has already zeroed it, e.g. on another stream)
+int scatter_dense_launch(const void* feat, int32_t in_kind, float in_scale, const int32_t* coords,
+                         const uint32_t* n_ptr, uint32_t launch_rows, int32_t channels,
+                         int32_t batch, const int32_t grid[3], const int32_t perm[3], void* out,
+                         bool clear, void* stream);
+int scatter_dense_layout_launch(const void* feat, int32_t in_kind, float in_scale,
+                                const int32_t* coords, const uint32_t* n_ptr, uint32_t launch_rows,
+                                int32_t channels, int32_t batch, const int32_t grid[3],
+                                const int32_t perm[3], int32_t layout, int32_t out_kind,
+                                float inv_out_scale, void* out, bool clear, void* stream);
 
 enum OpKind { OP_INPUT, OP_CONV, OP_ADD, OP_RELU, OP_DENSE, OP_RESHAPE, OP_TRANSPOSE };
 
