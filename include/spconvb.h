@@ -80,7 +80,9 @@ SPCONVB_API const char* spconvb_error_string(int code);
  * (libraries/3DSparseConvolution/libspconv/include/spconv/engine.hpp:135-156). */
 
 /* Number of 8-byte slots of the coordinate hash table for `cap_rows` rows
- * (power of two, load factor <= 0.5). */
+ * (power of two >= 1024, load factor <= 0.5).  A table passed to the functions below must
+ * have a power-of-two number of slots >= 8; its contents are opaque (the 8 cells of an
+ * aligned run along the innermost axis share one 64-byte block of slots). */
 SPCONVB_API uint32_t spconvb_hash_slots(uint32_t cap_rows);
 
 /* Insert rows 0..*n_ptr-1 of `coords` into `table` (slot = (key+1)<<32 | row,

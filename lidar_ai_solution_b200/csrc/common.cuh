@@ -57,12 +57,21 @@ __device__ __forceinline__ void set_status(uint32_t* status, uint32_t bit, uint3
   }
 }
 
-// slot = (key+1) << 32 | row ; 0 = empty.  Probe count is bounded by `slots`.
+// slot = (key+1) << 32 | row ; 0 = empty.  The table is a sequence of blocks of 8 slots (one
+// 64-byte line each): the 8 cells of an aligned run along the innermost axis hash to the same
+// block and take the slot of their position in the run, so the three x-neighbours a 3-wide
+// kernel asks for lie in one line (two when the run ends between them) instead of three
+// random ones.  A collision moves on block by block, same position.  Probe count is bounded
+// by the number of blocks.  `mask` = slots - 1, slots a power of two >= 8.
+__device__ __forceinline__ uint32_t hash_first_slot(uint32_t key, uint32_t mask) {
+  return ((hash32(key >> 3) & (mask >> 3)) << 3) | (key & 7u);
+}
+
 __device__ __forceinline__ int hash_insert(uint64_t* table, uint32_t mask, uint32_t key,
                                            uint32_t row, uint32_t* status) {
   const uint64_t packed = ((uint64_t)(key + 1u) << 32) | row;
-  uint32_t s = hash32(key) & mask;
-  for (uint32_t probe = 0; probe <= mask; ++probe) {
+  uint32_t s = hash_first_slot(key, mask);
+  for (uint32_t probe = 0; probe <= (mask >> 3); ++probe) {
     unsigned long long old =
         atomicCAS((unsigned long long*)(table + s), 0ull, (unsigned long long)packed);
     if (old == 0ull) return 0;
@@ -70,7 +79,7 @@ __device__ __forceinline__ int hash_insert(uint64_t* table, uint32_t mask, uint3
       set_status(status, SPCONVB_ST_DUPLICATE, row);
       return 1;
     }
-    s = (s + 1) & mask;
+    s = (s + 8u) & mask;
   }
   set_status(status, SPCONVB_ST_HASH_FULL, row);
   return 2;
@@ -78,12 +87,12 @@ __device__ __forceinline__ int hash_insert(uint64_t* table, uint32_t mask, uint3
 
 __device__ __forceinline__ int32_t hash_lookup(const uint64_t* __restrict__ table, uint32_t mask,
                                                uint32_t key) {
-  uint32_t s = hash32(key) & mask;
-  for (uint32_t probe = 0; probe <= mask; ++probe) {
+  uint32_t s = hash_first_slot(key, mask);
+  for (uint32_t probe = 0; probe <= (mask >> 3); ++probe) {
     uint64_t v = __ldg((const unsigned long long*)(table + s));
     if (v == 0ull) return -1;
     if ((uint32_t)(v >> 32) == key + 1u) return (int32_t)(uint32_t)v;
-    s = (s + 1) & mask;
+    s = (s + 8u) & mask;
   }
   return -1;
 }

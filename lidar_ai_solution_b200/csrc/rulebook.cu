@@ -568,7 +568,7 @@ int spconvb_hash_build(const int32_t* coords, const uint32_t* n_ptr, uint32_t ca
                        uint64_t* table, uint32_t slots, uint32_t flags, uint32_t* status,
                        void* stream) {
   if (!coords || !n_ptr || !table || !grid) return SPCONVB_E_ARG;
-  if (slots < 2 || (slots & (slots - 1)) || slots < 2ull * cap) return SPCONVB_E_ARG;
+  if (slots < 8 || (slots & (slots - 1)) || slots < 2ull * cap) return SPCONVB_E_ARG;
   if (!grid_fits(grid, batch)) return SPCONVB_E_RANGE;
   cudaStream_t st = (cudaStream_t)stream;
   if (!(flags & SPCONVB_FLAG_PREZEROED))
@@ -586,7 +586,7 @@ int spconvb_subm_map(const int32_t* coords, const uint32_t* n_ptr, uint32_t cap,
                      uint32_t slots, int32_t* map, uint32_t* status, void* stream) {
   (void)status;
   if (!coords || !n_ptr || !table || !map || !grid || !ksize || !dilation) return SPCONVB_E_ARG;
-  if (slots < 2 || (slots & (slots - 1))) return SPCONVB_E_ARG;
+  if (slots < 8 || (slots & (slots - 1))) return SPCONVB_E_ARG;
   if (!grid_fits(grid, batch)) return SPCONVB_E_RANGE;
   Kernel3 kr;
   for (int a = 0; a < 3; ++a) {
@@ -721,7 +721,7 @@ static int down_map_impl(const int32_t* in_coords, const uint32_t* n_in_ptr, uin
   if (!in_coords || !n_in_ptr || !in_grid || !ksize || !stride || !pad || !dilation ||
       !workspace || !out_coords || !n_out_ptr || !map)
     return SPCONVB_E_ARG;
-  if (out_table && (out_slots < 2 || (out_slots & (out_slots - 1)) || out_slots < 2ull * cap_out))
+  if (out_table && (out_slots < 8 || (out_slots & (out_slots - 1)) || out_slots < 2ull * cap_out))
     return SPCONVB_E_ARG;
   if (!grid_fits(in_grid, batch)) return SPCONVB_E_RANGE;
   Kernel3 kr;
@@ -831,7 +831,7 @@ int spconvb_down_map_static(const int32_t* in_coords, const uint32_t* n_in_ptr, 
   if (!in_coords || !n_in_ptr || !in_grid || !ksize || !stride || !pad || !dilation ||
       !out_coords || !n_out_ptr || !map)
     return SPCONVB_E_ARG;
-  if (out_table && (out_slots < 2 || (out_slots & (out_slots - 1)) || out_slots < 2ull * cap_out))
+  if (out_table && (out_slots < 8 || (out_slots & (out_slots - 1)) || out_slots < 2ull * cap_out))
     return SPCONVB_E_ARG;
   if (!grid_fits(in_grid, batch)) return SPCONVB_E_RANGE;
   int32_t og[3];
