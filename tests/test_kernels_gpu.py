@@ -144,6 +144,43 @@ def test_stage_chain_matches_oracle_and_fixture_counts(golden_dir):
             c_ref = roc
 
 
+@pytest.mark.parametrize("k,s,p,d", [
+    ((3, 3, 3), (2, 2, 2), (1, 1, 1), (1, 1, 1)),   # every strided layer of the backbones
+    ((3, 3, 3), (3, 3, 3), (0, 0, 0), (1, 1, 1)),   # stride that is not a power of two
+    ((5, 3, 1), (2, 1, 3), (2, 0, 1), (1, 1, 1)),   # mixed extents, stride 1 on an axis
+    ((2, 2, 2), (2, 2, 2), (0, 0, 0), (1, 1, 1)),   # even kernel
+    ((1, 1, 1), (2, 2, 2), (0, 0, 0), (1, 1, 1)),   # pure subsampling
+    ((3, 3, 7), (1, 2, 1), (1, 1, 3), (1, 1, 1)),   # runs of up to 7 adjacent output cells
+    ((3, 3, 3), (2, 2, 2), (2, 1, 2), (2, 1, 2)),   # dilated: the tap-pruning path
+])
+def test_down_map_geometries_match_the_oracle(k, s, p, d):
+    """Output coordinates, their order, the count and the whole map of a strided rulebook for
+    kernel / stride / padding / dilation combinations beyond the backbones', from the caller's
+    rows (input-side scatter) and again from rulebook-made rows (output-side lookup)."""
+    ops = _ops()
+    grid = (9, 70, 83)
+    coords = scenes.make_coords(6000, grid, 5)
+    st = ops.new_status()
+    dc = _dev(coords)
+    oc, n_out, dm, _, og, ws = ops.down_map(dc, ops.device_count(len(coords)), grid, None, k, s, p,
+                                            dilation=d, status=st, want_table=False,
+                                            return_ws=True)
+    roc, rdm, pairs, rog, rn = orc.down_map(coords, grid, k, s, p, d, cap=oc.shape[0])
+    _status_ok(st)
+    assert int(n_out.item()) == rn and list(og) == list(rog) and pairs > 0
+    assert np.array_equal(oc.cpu().numpy()[:rn], roc)
+    assert np.array_equal(dm.cpu().numpy()[:, :rn], rdm[:, :rn])
+    # second level: the rows just made are the input, looked up by rank from the output side
+    k2, s2, p2 = (3, 3, 3), (2, 2, 2), (1, 1, 1)
+    oc2, n2, dm2, _, og2 = ops.down_map(oc, n_out, og, None, k2, s2, p2, status=st,
+                                        want_table=False, in_ws=ws)
+    roc2, rdm2, _, rog2, rn2 = orc.down_map(roc, rog, k2, s2, p2, cap=oc2.shape[0])
+    _status_ok(st)
+    assert int(n2.item()) == rn2 and list(og2) == list(rog2)
+    assert np.array_equal(oc2.cpu().numpy()[:rn2], roc2)
+    assert np.array_equal(dm2.cpu().numpy()[:, :rn2], rdm2[:, :rn2])
+
+
 def test_down_map_overflow_sets_status():
     ops = _ops()
     from lidar_ai_solution_b200 import cabi
