@@ -80,7 +80,10 @@ static UmmaConfig choose_config(int rb, int cout, int kvol) {
   static const int force_m = env_int("SPCONVB_CONV_M", 0);
   static const int force_res = env_int("SPCONVB_CONV_RESIDENT", -1);
   static const int force_stages = env_int("SPCONVB_CONV_STAGES", 0);
-  static const int prefetch = env_int("SPCONVB_CONV_PREFETCH", 3);
+  // Off by default: with the current producers the bulk L2 prefetch of a tile's map lines,
+  // input rows and residual rows costs 1-4 % at every batch size (it was worth 3-5 % before the
+  // indices moved into registers and the producers were split into two groups).
+  static const int prefetch = env_int("SPCONVB_CONV_PREFETCH", 0);
   const int nchunk = (kvol * rb + kChunk - 1) / kChunk;
   const int full = 128 / cout, half = cout <= 64 ? 64 / cout : 0;
   auto best_stages = [&](int rep, int resident) {
