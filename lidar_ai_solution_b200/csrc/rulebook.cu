@@ -215,6 +215,70 @@ __global__ void down_mark_kernel(const int4* __restrict__ coords, const uint32_t
   }
 }
 
+// Up to 64 bits of a bitmap starting at cell `line + x0` of a line of `gx` cells that starts
+// at linear cell `line`: bit i of the result is cell x0 + i, zero outside the line.
+__device__ __forceinline__ unsigned long long line_bits64(const uint32_t* __restrict__ bitmap,
+                                                          uint32_t words, uint32_t line, int x0,
+                                                          int count, int gx) {
+  const int lo = max(x0, 0), hi = min(x0 + count - 1, gx - 1);
+  if (lo > hi) return 0ull;
+  const uint32_t start = line + (uint32_t)lo, w = start >> 5, off = start & 31u;
+  unsigned long long v = (unsigned long long)__ldg(bitmap + w) >> off;
+  if (w + 1 < words) v |= (unsigned long long)__ldg(bitmap + w + 1) << (32u - off);
+  if (off && w + 2 < words) v |= (unsigned long long)__ldg(bitmap + w + 2) << (64u - off);
+  const int nb = hi - lo + 1;
+  if (nb < 64) v &= (1ull << nb) - 1ull;
+  return v << (lo - x0);
+}
+
+// The mark step when the input rows were made by a strided rulebook themselves: the output
+// bitmap is computed from the input's bitmap, 16 output cells of one line per thread.  Output
+// cell o is set when any input cell of its window (o * stride - pad + [0, K) per axis, dilation
+// 1) is set: the K0 x K1 input lines that matter are OR-ed as bit strings, then each output
+// bit tests its K2-wide piece.  No rows are read, no two threads fight for a word (the two
+// atomics per thread only merge neighbouring segments of a word).  Input cells whose rank is
+// beyond the capacity of the input rows (an overflow the rulebook that made them has already
+// reported) count as set.
+constexpr int kMarkCells = 16;
+__global__ void down_mark_ranked_kernel(const uint32_t* __restrict__ in_bitmap, uint32_t in_words,
+                                        Grid3 gin, Grid3 gout, Kernel3 kr,
+                                        uint32_t* __restrict__ out_bitmap) {
+  const int segs = (gout.g[2] + kMarkCells - 1) / kMarkCells;
+  const unsigned long long lines = (unsigned long long)gout.batch * gout.g[0] * gout.g[1];
+  const unsigned long long kmask = (1ull << kr.k[2]) - 1ull;
+  for (unsigned long long item = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
+       item < lines * segs; item += (unsigned long long)gridDim.x * blockDim.x) {
+    const unsigned long long line = item / segs;
+    const int ox0 = (int)(item - line * segs) * kMarkCells;
+    const int ncell = min(kMarkCells, gout.g[2] - ox0);
+    const int o1 = (int)(line % gout.g[1]);
+    const int o0 = (int)((line / gout.g[1]) % gout.g[0]);
+    const int b = (int)(line / ((unsigned long long)gout.g[1] * gout.g[0]));
+    const int x0 = ox0 * kr.s[2] - kr.p[2];
+    const int count = (ncell - 1) * kr.s[2] + kr.k[2];  // <= 64 (checked by the launcher)
+    unsigned long long win = 0ull;
+    for (int k0 = 0; k0 < kr.k[0]; ++k0) {
+      const int i0 = o0 * kr.s[0] - kr.p[0] + k0;
+      if ((unsigned)i0 >= (unsigned)gin.g[0]) continue;
+      for (int k1 = 0; k1 < kr.k[1]; ++k1) {
+        const int i1 = o1 * kr.s[1] - kr.p[1] + k1;
+        if ((unsigned)i1 >= (unsigned)gin.g[1]) continue;
+        win |= line_bits64(in_bitmap, in_words, voxel_key(b, i0, i1, 0, gin), x0, count, gin.g[2]);
+      }
+    }
+    if (!win) continue;
+    uint32_t r = 0;
+#pragma unroll
+    for (int i = 0; i < kMarkCells; ++i)
+      if (i < ncell && ((win >> (i * kr.s[2])) & kmask)) r |= 1u << i;
+    if (!r) continue;
+    const uint32_t cell = (uint32_t)(line * gout.g[2]) + (uint32_t)ox0;
+    const unsigned long long run = (unsigned long long)r << (cell & 31u);
+    atomicOr(out_bitmap + (cell >> 5), (uint32_t)run);
+    if (run >> 32) atomicOr(out_bitmap + (cell >> 5) + 1, (uint32_t)(run >> 32));
+  }
+}
+
 // Row of an output cell from the bitmap and its (global) popcount prefix, -1 if
 // the cell is not an output or lies beyond the capacity.
 __device__ __forceinline__ int32_t rank_lookup(const uint32_t* __restrict__ bitmap,
@@ -751,8 +815,19 @@ static int down_map_impl(const int32_t* in_coords, const uint32_t* n_in_ptr, uin
   }
   Grid3 gin = make_grid(in_grid, batch), gout = make_grid(og, batch);
   if (launch_rows == 0 || launch_rows > cap_in) launch_rows = cap_in;
-  down_mark_kernel<<<flat_blocks(launch_rows), kThreads, 0, st>>>(
-      (const int4*)in_coords, n_in_ptr, cap_in, gin, gout, kr, ws.bitmap);
+  // rows made by a rulebook: their bitmap gives the outputs' bitmap directly (when a
+  // thread's window of input cells fits 64 bits)
+  const bool from_bitmap = in_workspace && unit_dilation(kr) && kr.k[2] <= 32 &&
+                           (kMarkCells - 1) * kr.s[2] + kr.k[2] <= 64;
+  if (from_bitmap) {
+    const unsigned long long items = (unsigned long long)batch * og[0] * og[1] *
+                                     (unsigned long long)((og[2] + kMarkCells - 1) / kMarkCells);
+    down_mark_ranked_kernel<<<flat_blocks(items), kThreads, 0, st>>>(
+        (const uint32_t*)in_workspace, down_words(in_grid, batch), gin, gout, kr, ws.bitmap);
+  } else {
+    down_mark_kernel<<<flat_blocks(launch_rows), kThreads, 0, st>>>(
+        (const int4*)in_coords, n_in_ptr, cap_in, gin, gout, kr, ws.bitmap);
+  }
   SPCONVB_LAUNCH_CHECK();
   down_scan_kernel<<<ws.blocks, kScanThreads, 0, st>>>(ws);
   SPCONVB_LAUNCH_CHECK();
