@@ -506,6 +506,32 @@ def test_batched_forward_equals_frame_by_frame():
         assert torch.equal(got[b], want[i][0]), "frame %d in slot %d" % (i, b)
 
 
+def test_a_frame_without_rows_inside_a_batch():
+    """Three frame slots, the middle one empty: its dense slice is all zeros, the other two are
+    the bits of single-frame calls, no status bit is set."""
+    eng = _engine_mod()
+    frames = [_frame(7000, seed=21), _frame(5000, seed=22)]
+    model = _quantized("centerpoint", *frames[0], seed=21)
+    one = eng.Engine.from_model(model, eng.PRECISION_INT8, 0)
+    want = []
+    for f, c in frames:
+        one.forward(_dev(f), _dev(c), GRID)
+        torch.cuda.synchronize()
+        want.append(one.output(0).clone())
+    feats = np.concatenate([f for f, _ in frames])
+    coords = np.concatenate([np.concatenate([np.full((len(c), 1), b, np.int32), c[:, 1:]], 1)
+                             for b, (_, c) in zip((0, 2), frames)])
+    many = eng.Engine.from_model(model, eng.PRECISION_INT8, 0)
+    many.prepare(GRID, 3)
+    many.forward(_dev(feats), _dev(coords), GRID, batch=3)
+    torch.cuda.synchronize()
+    assert many.status()[0] == 0
+    got = many.output(0)
+    assert got.shape[0] == 3
+    assert torch.equal(got[0], want[0][0]) and torch.equal(got[2], want[1][0])
+    assert float(got[1].abs().max()) == 0.0
+
+
 def test_row_count_beyond_the_buffers_sets_status_and_touches_nothing_else():
     """DDS with a device-side row count larger than the caller's buffers: every kernel clamps
     to the capacity it was given, the overflow bit is set, and memory behind the feature rows
