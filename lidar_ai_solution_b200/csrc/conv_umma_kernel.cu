@@ -40,10 +40,10 @@
 //               A producer never waits for its copies: every thread lets them
 //               arrive on the stage's mbarrier when they land, so all free stages
 //               of the ring are in flight.  One thread also streams the
-//               pre-swizzled weight chunk with one bulk async copy, and a few
+//               pre-swizzled weight chunk with one bulk async copy.  Optionally
+//               (UmmaArgs.prefetch > 0; off by default, it measured slower) a few
 //               lanes ask L2 (bulk prefetch) for the map lines, input rows and
-//               residual rows of the tile the CTA will reach some rounds later,
-//               so that the gathers find them in L2 instead of HBM.
+//               residual rows of the tile the CTA will reach some rounds later.
 //
 // K is walked in chunks of 128 bytes (one swizzle atom per row): a chunk is 8
 // taps of a 16-byte row, ..., 1 tap of a 128-byte row, or half a 256-byte row.
