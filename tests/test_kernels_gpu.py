@@ -179,6 +179,22 @@ def test_down_map_geometries_match_the_oracle(k, s, p, d):
     assert int(n2.item()) == rn2 and list(og2) == list(rog2)
     assert np.array_equal(oc2.cpu().numpy()[:rn2], roc2)
     assert np.array_equal(dm2.cpu().numpy()[:, :rn2], rdm2[:, :rn2])
+    # and the geometry under test on rulebook-made rows (the outputs' bitmap then comes from
+    # the inputs' bitmap): first a 3x3x3 stride-1 rulebook over the caller's rows, whose
+    # outputs are ranked, then the geometry on those
+    fo, fn, _, _, fg, fws = ops.down_map(dc, ops.device_count(len(coords)), grid, None, (3, 3, 3),
+                                         (1, 1, 1), (1, 1, 1), status=st, want_table=False,
+                                         return_ws=True)
+    rfo, _, _, rfg, rfn = orc.down_map(coords, grid, (3, 3, 3), (1, 1, 1), (1, 1, 1),
+                                       cap=fo.shape[0])
+    assert int(fn.item()) == rfn
+    oc3, n3, dm3, _, og3 = ops.down_map(fo, fn, fg, None, k, s, p, dilation=d, status=st,
+                                        want_table=False, in_ws=fws)
+    roc3, rdm3, _, rog3, rn3 = orc.down_map(rfo, rfg, k, s, p, d, cap=oc3.shape[0])
+    _status_ok(st)
+    assert int(n3.item()) == rn3 and list(og3) == list(rog3)
+    assert np.array_equal(oc3.cpu().numpy()[:rn3], roc3)
+    assert np.array_equal(dm3.cpu().numpy()[:, :rn3], rdm3[:, :rn3])
 
 
 def test_down_map_overflow_sets_status():
